@@ -1,0 +1,134 @@
+/*
+ * tb200.h — C ABI of the B200-native `cuda` backend for TileBench's quantized-inference path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*, i.e. a
+ * cudaStream_t; NULL = the legacy default stream).  Unless a comment says otherwise an entry point
+ *   - validates its arguments on the host and returns a nonzero TB200_ERR_* code instead of launching,
+ *   - enqueues its kernels on `stream` and returns without synchronising,
+ *   - allocates nothing, so it may run under CUDA-graph capture (the reference's timer executes a
+ *     backend's run() under capture: tilebench/core/timer.py:120-143),
+ *   - never throws.  tb200_last_error() returns the message of the calling thread's last failure.
+ *
+ * The reference (TileBench) has no native code: its operator boundary is the Python function
+ * `run(*inputs, **kw)` of tilebench/benchmarks/operators/<op>/impl_<backend>.py, driven by
+ * tilebench/core/engine.py:337-366.  Each declaration below names the reference operator whose
+ * run() it stands behind, or says that the operator is new (int4 / W4A16 / block-scaled FP8 do not
+ * exist in the reference; they follow its operator contract).
+ */
+#ifndef TB200_H_
+#define TB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TB200_ABI_VERSION 1
+
+/* Return codes. */
+#define TB200_OK              0
+#define TB200_ERR_ARG         1  /* null pointer, non-positive size, unsupported divisibility     */
+#define TB200_ERR_ALIGN       2  /* pointer or leading dimension breaks a stated alignment         */
+#define TB200_ERR_UNSUPPORTED 3  /* dtype / shape combination the kernels do not implement         */
+#define TB200_ERR_CUDA        4  /* a CUDA runtime or driver call failed (message has the text)     */
+#define TB200_ERR_WORKSPACE   5  /* workspace missing or too small                                  */
+#define TB200_ERR_DEVICE      6  /* device is not sm_100 (B200)                                     */
+#define TB200_ERR_TIMEOUT     7  /* a bounded in-kernel wait ran out (read back by tb200_device_status) */
+
+/* Element types of tensors that cross the ABI. */
+#define TB200_DT_F32  0
+#define TB200_DT_F16  1
+#define TB200_DT_BF16 2
+
+int         tb200_abi_version(void);
+/* Message of the calling thread's most recent failing call ("" if none). */
+const char* tb200_last_error(void);
+/* 0 when the current device is compute capability 10.x, TB200_ERR_DEVICE otherwise. */
+int         tb200_check_device(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Streaming dequantisation (HBM-bound).
+ * ------------------------------------------------------------------------------------------- */
+
+/*
+ * Per-group int4 weight dequantisation (new operator `dequant_int4_group`; the nearest reference
+ * operator is weight_dequant, tilebench/benchmarks/operators/weight_dequant/impl_torch.py:4-8).
+ *   wp      uint8 [n, k/2]          two nibbles per byte, low nibble = even k
+ *   scales  fp16  [n, k/group]
+ *   out     fp16  [n, ldo] (ldo >= k, in elements)
+ *   out[r,c] = fp16( (q[r,c] - zero_point) * float(scales[r, c/group]) )   — one rounding, bit-exact
+ * k must be even and a multiple of group; group a multiple of 8 selects the 128-bit vector kernel.
+ */
+int tb200_dequant_int4_group(const void* wp, const void* scales, void* out,
+                             int64_t n, int64_t k, int64_t group, int zero_point,
+                             int64_t ldo, void* stream);
+
+/*
+ * Per-row int8 dequantisation.  Serves the new operator `dequant_int8_channel`
+ * (out = bf16(float(w) * scale[r])) and the reference operator dequantize_rowwise
+ * (tilebench/benchmarks/operators/dequantize_rowwise/impl_torch.py:4-7:
+ *  out = fp16((state_x[r] * float(x)) * float(1/127)), two fp32 roundings, in that order).
+ *   w      int8 [rows, cols]      scale  fp32 [rows]      out  out_dtype [rows, cols]
+ *   out_dtype  TB200_DT_F16 or TB200_DT_BF16
+ *   use_post   nonzero: multiply the fp32 product by `post` (a second fp32 rounding) before the cast
+ */
+int tb200_dequant_int8_rowwise(const void* w, const float* scale, void* out,
+                               int64_t rows, int64_t cols, int out_dtype,
+                               int use_post, float post, void* stream);
+
+/*
+ * Float block-scale multiply — the reference operator weight_dequant
+ * (tilebench/benchmarks/operators/weight_dequant/impl_torch.py:4-8): Y[i,j] = X[i,j] * S[i/T, j/T],
+ * X, S, Y of one dtype (TB200_DT_F32 / F16 / BF16), S of shape [ceil(M/T), ceil(N/T)].
+ */
+int tb200_weight_dequant_block(const void* x, const void* s, void* y,
+                               int64_t m, int64_t n, int64_t tile, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Quantised GEMMs on tcgen05 tensor cores (TMA operands, TMEM accumulators).
+ * ------------------------------------------------------------------------------------------- */
+
+/*
+ * FP8 e4m3 block-scaled GEMM (new operator `gemm_fp8_blockscaled`; the nearest reference operator
+ * is the unit-scale fp8 branch of tilebench/benchmarks/operators/matmul_fp32_fp16_fp8/impl_torch.py:21-27).
+ *   a   e4m3 [m, k]   sa fp32 [m, k/128]          (one scale per 1x128 block of A)
+ *   b   e4m3 [n, k]   sb fp32 [n/128, k/128]      (one scale per 128x128 block of B)
+ *   out bf16 [m, ldo] = bf16( sum_kb sa[i,kb] * sb[j/128,kb] * dot(a[i,kb*128:+128], b[j,kb*128:+128]) )
+ * fp32 accumulation.  m, n multiples of 128, k a multiple of 128; a, b, out 16-byte aligned.
+ */
+int tb200_gemm_fp8_blockscaled(const void* a, const float* sa, const void* b, const float* sb,
+                               void* out, int64_t m, int64_t n, int64_t k, int64_t ldo,
+                               void* stream);
+
+/*
+ * W4A16 dequant-fused GEMM (new operator `gemm_w4a16`; structural template: the packed-weight
+ * GEMM tilebench/benchmarks/operators/matmul_int8/impl_torch.py:4-19).
+ *   a       fp16  [m, k]
+ *   wp      uint8 [n, k/2], scales fp16 [n, k/group]   as in tb200_dequant_int4_group (group = 128)
+ *   out     fp16  [m, ldo]; this call writes columns [col_offset, col_offset + n) — an N-partitioned
+ *           rank passes its slice of wp/scales and the offset of its slice in the full output
+ *   out[i, col_offset + j] = fp16( sum_k float(a[i,k]) * float(fp16((q[j,k]-zp) * scales[j,k/group])) )
+ *   workspace  fp32 scratch for the split-K variant chosen for small m; size from
+ *              tb200_gemm_w4a16_workspace_bytes(); may be NULL when that returns 0
+ * n a multiple of 128, k a multiple of 128.
+ */
+size_t tb200_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int    tb200_gemm_w4a16(const void* a, const void* wp, const void* scales, void* out,
+                        int64_t m, int64_t n, int64_t k, int64_t group, int zero_point,
+                        int64_t ldo, int64_t col_offset,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Device status word.  Every wait inside the GEMM kernels (mbarrier, TMEM hand-off) is bounded;
+ * a wait that runs out records a code here and the kernel drains and returns instead of hanging.
+ * These two calls synchronise the device and must stay outside timed regions and graph capture.
+ * ------------------------------------------------------------------------------------------- */
+int tb200_device_status(int* code, int* detail);   /* code 0 = clean */
+int tb200_clear_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TB200_H_ */

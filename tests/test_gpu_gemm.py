@@ -1,0 +1,172 @@
+"""GPU parity of the tcgen05 GEMMs against the CPU oracle, within the operator's stated tolerance
+(fp16: atol 1e-3 / rtol 1e-3; bf16: atol 1e-2 / rtol 1.6e-2), plus exact known-answer cases."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_ops
+from tilebench_b200 import native
+from tilebench_b200.data import tensors
+
+pytestmark = pytest.mark.gpu
+
+FP16_TOL = dict(atol=1e-3, rtol=1e-3)
+BF16_TOL = dict(atol=1e-2, rtol=1.6e-2)
+
+
+def status_clean():
+    code, detail = native.device_status()
+    assert code == 0, f"kernel wait timed out: code {code} detail {detail}"
+
+
+def u8(t):
+    return t.view(torch.uint8).cpu().numpy()
+
+
+# ---------------------------------------------------------------- FP8 block-scaled
+
+def fp8_case(M, N, K, seed, device):
+    aq, sa, bq, sb = tensors.generate_gemm_fp8_blockscaled_inputs(M=M, N=N, K=K, device="cpu", seed=seed)
+    from tilebench_b200.benchmarks.operators.gemm_fp8_blockscaled import impl_cuda
+    native.clear_device_status()
+    out = impl_cuda.run(aq.to(device), sa.to(device), bq.to(device), sb.to(device))
+    torch.cuda.synchronize()
+    status_clean()
+    want = ref_ops.bf16_bits_to_f32(ref_ops.gemm_fp8_blockscaled(u8(aq), sa.numpy(), u8(bq), sb.numpy()))
+    return out.float().cpu().numpy(), want
+
+
+def test_fp8_small_integers_exact(cuda_device):
+    """Small integer operands and power-of-two scales: every partial sum is exact, so the result
+    must equal the oracle bit for bit — this pins the operand layout (swizzle, descriptors, K order)."""
+    from tilebench_b200.benchmarks.operators.gemm_fp8_blockscaled import impl_cuda
+    g = torch.Generator().manual_seed(0)
+    M, N, K = 128, 128, 256
+    a = torch.randint(-3, 4, (M, K), generator=g).float()
+    b = torch.randint(-3, 4, (N, K), generator=g).float()
+    aq, bq = a.to(torch.float8_e4m3fn), b.to(torch.float8_e4m3fn)
+    sa = torch.tensor([0.5, 2.0]).repeat(M, 1)
+    sb = torch.tensor([[4.0, 0.25]])
+    native.clear_device_status()
+    out = impl_cuda.run(aq.to(cuda_device), sa.to(cuda_device), bq.to(cuda_device), sb.to(cuda_device))
+    torch.cuda.synchronize()
+    status_clean()
+    want = ref_ops.gemm_fp8_blockscaled(u8(aq), sa.numpy(), u8(bq), sb.numpy())
+    got = out.cpu().view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (1024, 1024, 1024), (200, 256, 384), (1, 128, 128)])
+def test_fp8_matches_oracle_n128_tiles(cuda_device, M, N, K):
+    got, want = fp8_case(M, N, K, seed=M + N + K, device=cuda_device)
+    np.testing.assert_allclose(got, want, **BF16_TOL)
+
+
+def test_fp8_matches_oracle_n256_tiles(cuda_device):
+    # 32 x 20 = 640 tiles of 128 x 256 >= 148: takes the wide-tile kernel, several tiles per CTA
+    got, want = fp8_case(4096, 5120, 512, seed=21, device=cuda_device)
+    np.testing.assert_allclose(got, want, **BF16_TOL)
+
+
+def test_fp8_4096_cube_vs_torch_reference(cuda_device):
+    from tilebench_b200.benchmarks.operators.gemm_fp8_blockscaled import impl_cuda, impl_torch
+    inputs = tensors.generate_gemm_fp8_blockscaled_inputs(S=4096, device=cuda_device, seed=5)
+    native.clear_device_status()
+    out = impl_cuda.run(*inputs)
+    torch.cuda.synchronize()
+    status_clean()
+    torch.testing.assert_close(out, impl_torch.run(*inputs), **BF16_TOL)
+    again = impl_cuda.run(*inputs)
+    assert torch.equal(out, again)                      # run-to-run deterministic
+
+
+def test_fp8_rejects_bad_shapes(cuda_device):
+    ext = native.load()
+    a = torch.zeros(128, 192, device=cuda_device).to(torch.float8_e4m3fn)
+    with pytest.raises(Exception):
+        ext.gemm_fp8_blockscaled(a, torch.ones(128, 1, device=cuda_device), a, torch.ones(1, 1, device=cuda_device),
+                                 torch.empty(128, 128, dtype=torch.bfloat16, device=cuda_device))
+
+
+# ---------------------------------------------------------------- W4A16
+
+def w4_case(M, N, K, seed, device, group=128):
+    from tilebench_b200.benchmarks.operators.gemm_w4a16 import impl_cuda
+    a, wp, sc, group, zp = tensors.generate_gemm_w4a16_inputs(M, K, N, GROUP=group, device="cpu", seed=seed)
+    native.clear_device_status()
+    out = impl_cuda.run(a.to(device), wp.to(device), sc.to(device), group, zp)
+    torch.cuda.synchronize()
+    status_clean()
+    want = ref_ops.gemm_w4a16(a.numpy(), wp.numpy(), sc.numpy(), group, zp)
+    return out.float().cpu().numpy(), want.astype(np.float32)
+
+
+def test_w4a16_one_hot_rows_read_out_weight_columns_exactly(cuda_device):
+    """Activation row i is one-hot at column k_i: the output row must be the dequantised weight
+    column k_i, bit for bit — pins nibble order, group scales, TMEM operand layout and K order."""
+    from tilebench_b200.benchmarks.operators.gemm_w4a16 import impl_cuda
+    N, K, M = 256, 512, 128
+    wp, sc = tensors.make_int4_group_weights(N, K, 128, seed=3)
+    ks = torch.randperm(K, generator=torch.Generator().manual_seed(1))[:M]
+    a = torch.zeros(M, K, dtype=torch.float16)
+    a[torch.arange(M), ks] = 1.0
+    native.clear_device_status()
+    out = impl_cuda.run(a.to(cuda_device), wp.to(cuda_device), sc.to(cuda_device), 128, 8)
+    torch.cuda.synchronize()
+    status_clean()
+    w = ref_ops.dequant_int4_group(wp.numpy(), sc.numpy(), 128, 8)          # [N, K] fp16
+    want = w[:, ks.numpy()].T
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), np.ascontiguousarray(want).view(np.uint16))
+
+
+@pytest.mark.parametrize("M", [1, 3, 16, 17, 64, 127, 128, 129, 300])
+def test_w4a16_matches_oracle_across_m(cuda_device, M):
+    got, want = w4_case(M, 512, 1024, seed=40 + M, device=cuda_device)
+    np.testing.assert_allclose(got, want, **FP16_TOL)
+
+
+@pytest.mark.parametrize("M", [1, 16, 128])
+def test_w4a16_config_shapes_small_m(cuda_device, M):
+    got, want = w4_case(M, 14336, 4096, seed=50 + M, device=cuda_device)
+    np.testing.assert_allclose(got, want, **FP16_TOL)
+
+
+def test_w4a16_config_shape_m4096_vs_torch_reference(cuda_device):
+    from tilebench_b200.benchmarks.operators.gemm_w4a16 import impl_cuda, impl_torch
+    inputs = tensors.generate_gemm_w4a16_inputs(4096, 4096, 14336, device=cuda_device, seed=6)
+    native.clear_device_status()
+    out = impl_cuda.run(*inputs)
+    torch.cuda.synchronize()
+    status_clean()
+    torch.testing.assert_close(out, impl_torch.run(*inputs), **FP16_TOL)
+    assert torch.equal(out, impl_cuda.run(*inputs))     # deterministic, split-K or not
+
+
+def test_w4a16_column_offset_writes_only_its_slice(cuda_device):
+    """N-partition building block: two calls with col_offset fill one [M, N] buffer; guard columns stay."""
+    ext = native.load()
+    M, N, K = 64, 512, 512
+    a, wp, sc, group, zp = tensors.generate_gemm_w4a16_inputs(M, K, N, device="cpu", seed=8)
+    ad, wpd, scd = a.to(cuda_device), wp.to(cuda_device), sc.to(cuda_device)
+    out = torch.full((M, N + 64), 7.0, dtype=torch.float16, device=cuda_device)
+    half = N // 2
+    for r in range(2):
+        n_local = half
+        wsb = ext.gemm_w4a16_workspace_bytes(M, n_local, K)
+        ws = torch.empty(max(wsb // 4, 1), dtype=torch.float32, device=cuda_device)
+        ext.gemm_w4a16(ad, wpd[r * half:(r + 1) * half].contiguous(), scd[r * half:(r + 1) * half].contiguous(),
+                       out, group, zp, r * half, ws)
+    torch.cuda.synchronize()
+    want = ref_ops.gemm_w4a16(a.numpy(), wp.numpy(), sc.numpy(), group, zp).astype(np.float32)
+    np.testing.assert_allclose(out[:, :N].float().cpu().numpy(), want, **FP16_TOL)
+    assert torch.all(out[:, N:] == 7.0)
+
+
+def test_w4a16_workspace_too_small_is_an_error(cuda_device):
+    ext = native.load()
+    a, wp, sc, group, zp = tensors.generate_gemm_w4a16_inputs(1, 4096, 14336, device=cuda_device, seed=9)
+    if ext.gemm_w4a16_workspace_bytes(1, 14336, 4096) == 0:
+        pytest.skip("no split-K for this shape")
+    out = torch.empty(1, 14336, dtype=torch.float16, device=cuda_device)
+    with pytest.raises(ValueError):
+        ext.gemm_w4a16(a, wp, sc, out, group, zp, 0, None)

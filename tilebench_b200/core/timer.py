@@ -1,0 +1,118 @@
+"""Device-side timing of one operator call.
+
+Protocol of the reference timer (tilebench/core/timer.py:208-284): `warmup` untimed calls, then
+`repeat` timed calls, each preceded — outside the timed region — by a write of 2x the L2 size so
+the call starts cold; with `use_cuda_graph` the call is captured once and the replay is timed
+(capture failure falls back to eager, as in timer.py:129-143).  The reference sums kernel
+durations with the Proton profiler; here the timed quantity is a CUDA-event pair around each call
+on the launching stream, which adds the launch gap of the first kernel (a few microseconds) to
+very short operators.  `report_benchmark_batched` amortises that gap for roofline numbers by
+timing back-to-back calls on rotating buffers whose combined footprint exceeds L2.
+"""
+from __future__ import annotations
+
+import statistics
+from typing import Any, Callable, Sequence
+
+import torch
+
+from tilebench_b200.hardware import B200_L2_BYTES, last_level_cache_bytes
+
+DEFAULT_WARMUP = 1
+DEFAULT_REPEAT = 3
+
+_flush_buf: torch.Tensor | None = None
+
+
+def effective_use_cuda_graph(requested: bool) -> bool:
+    return bool(requested)
+
+
+def timing_mode(requested: bool) -> dict[str, Any]:
+    eff = effective_use_cuda_graph(requested)
+    return {"requested_use_cuda_graph": bool(requested), "effective_use_cuda_graph": eff,
+            "timing_execution_mode": "graph" if eff else "eager", "timing_note": None,
+            "timer": "cuda_events"}
+
+
+def flush_buffer_bytes() -> int:
+    """2x the last-level cache (B200: 2 x 126.5 MB = 253 MB)."""
+    return 2 * (last_level_cache_bytes() or B200_L2_BYTES)
+
+
+def flush_l2_cache() -> None:
+    """Evict L2 by writing a buffer twice its size (enqueued on the current stream, no sync)."""
+    global _flush_buf
+    numel = flush_buffer_bytes() // 4
+    if _flush_buf is None or _flush_buf.numel() != numel:
+        _flush_buf = torch.empty(numel, device="cuda", dtype=torch.float32)
+    _flush_buf.fill_(1.0)
+
+
+def _prepare_runner(f: Callable, args: Sequence, kwargs: dict, use_cuda_graph: bool):
+    """Returns (runner, mode).  Graph mode: 3 eager calls on a side stream, then capture."""
+    if not use_cuda_graph:
+        return (lambda: f(*args, **kwargs)), "eager"
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                f(*args, **kwargs)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            f(*args, **kwargs)
+        return graph.replay, "graph"
+    except Exception:
+        torch.cuda.synchronize()
+        return (lambda: f(*args, **kwargs)), "eager"
+
+
+def report_benchmark(f: Callable, args: Sequence = (), kwargs: dict | None = None, *, warmup: int = DEFAULT_WARMUP,
+                     repeat: int = DEFAULT_REPEAT, use_cuda_graph: bool = False, flush_l2: bool = True,
+                     **_ignored) -> dict[str, Any]:
+    """Time `f(*args, **kwargs)`; returns {"mean", "median", "min", "max", "samples", "mode"} in ms."""
+    kwargs = kwargs or {}
+    do_flush = flush_l2
+    for _ in range(max(0, warmup)):
+        if do_flush:
+            flush_l2_cache()
+        f(*args, **kwargs)
+    torch.cuda.synchronize()
+    runner, mode = _prepare_runner(f, args, kwargs, use_cuda_graph)
+    samples = []
+    for _ in range(max(1, repeat)):
+        if do_flush:
+            flush_l2_cache()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner()
+        end.record()
+        end.synchronize()
+        samples.append(start.elapsed_time(end))
+    return {"mean": statistics.fmean(samples), "median": statistics.median(samples), "min": min(samples),
+            "max": max(samples), "samples": samples, "mode": mode}
+
+
+def report_benchmark_batched(launchers: Sequence[Callable[[], Any]], *, warmup: int = 3, repeat: int = 20) -> dict[str, Any]:
+    """Time back-to-back calls of `launchers` (one per rotating buffer set; together the sets must
+    exceed L2 so no call finds its inputs cached).  One event pair brackets a full rotation; the
+    per-call time is rotation time / len(launchers)."""
+    n = len(launchers)
+    for _ in range(max(0, warmup)):
+        for fn in launchers:
+            fn()
+    torch.cuda.synchronize()
+    samples = []
+    for _ in range(max(1, repeat)):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for fn in launchers:
+            fn()
+        end.record()
+        end.synchronize()
+        samples.append(start.elapsed_time(end) / n)
+    return {"mean": statistics.fmean(samples), "median": statistics.median(samples), "min": min(samples),
+            "max": max(samples), "samples": samples, "mode": f"batched x{n}"}

@@ -1,0 +1,400 @@
+// Streaming dequantisation kernels for sm_100a (HBM-bound):
+//   tb200_k_dequant_int4_group   packed int4 + fp16 group scales   -> fp16
+//   tb200_k_dequant_int8_rowwise int8 + fp32 row scale (+ post-mul) -> fp16 / bf16
+//   tb200_k_weight_dequant_*     float X * S[i/T, j/T]              -> same dtype
+// Shape of every vector kernel: a persistent grid (a multiple of the SM count) strides over
+// 16-byte output chunks; each thread first issues UNROLL independent loads, then unpacks in
+// registers and writes one 128-bit store per chunk, so every warp-level load and store is a
+// single contiguous segment.  Kernels are extern "C" so profilers list them by a bare name.
+#include "common.cuh"
+
+namespace tb200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+
+// Persistent launch: enough CTAs to fill every SM's thread slots, never more than the work needs.
+inline unsigned grid_for(uint64_t work_items, int threads, int unroll) {
+    uint64_t per_cta = static_cast<uint64_t>(threads) * unroll;
+    uint64_t need = (work_items + per_cta - 1) / per_cta;
+    uint64_t cap = static_cast<uint64_t>(num_sms()) * (2048 / threads);
+    if (need < 1) need = 1;
+    return static_cast<unsigned>(need < cap ? need : cap);
+}
+
+// Two nibbles of one byte -> half2 (low nibble first), exact:  h = 0x6400 | q  is 1024 + q.
+__device__ __forceinline__ __half2 nib_pair_to_half2(uint32_t lo_src, uint32_t hi_src, uint32_t sel) {
+    // byte `sel&7` of lo_src lands in bits 0-7, the same byte of hi_src (= lo_src >> 4) in bits 16-23
+    uint32_t w = __byte_perm(lo_src, hi_src, sel);
+    uint32_t h;
+    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(h) : "r"(w));  // (w & m) | c
+    return *reinterpret_cast<__half2*>(&h);
+}
+
+}  // namespace
+}  // namespace tb200
+
+using namespace tb200;
+
+// out[r, c] = fp16((q - zp) * s[r, c/group]);  one thread-chunk = 4 packed bytes = 8 outputs.
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_dequant_int4_group(const uint32_t* __restrict__ wp, const __half* __restrict__ scales,
+                           __half* __restrict__ out, uint32_t chunks_per_row, uint32_t group_chunks,
+                           uint32_t groups_per_row, uint64_t total_chunks, int64_t ldo, float zp_plus_1024) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+    const __half2 bias = __float2half2_rn(zp_plus_1024);  // 1024 + zero_point, exact for 0..15
+    for (uint64_t base = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; base < total_chunks;
+         base += stride * kUnroll) {
+        uint32_t packed[kUnroll];
+        __half sc[kUnroll];
+        uint64_t off[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            uint64_t c = base + u * stride;
+            if (c < total_chunks) {
+                uint64_t row = c / chunks_per_row;
+                uint32_t cc = static_cast<uint32_t>(c - row * chunks_per_row);
+                packed[u] = __ldg(wp + c);
+                sc[u] = __ldg(scales + row * groups_per_row + cc / group_chunks);
+                off[u] = row * static_cast<uint64_t>(ldo) + static_cast<uint64_t>(cc) * 8;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            uint64_t c = base + u * stride;
+            if (c < total_chunks) {
+                const uint32_t lo = packed[u], hi = packed[u] >> 4;
+                const __half2 s2 = __half2half2(sc[u]);
+                __half2 v[4];
+                // selector: result byte0 = byte i of lo, byte2 = byte i of hi (index 4+i); others masked
+                v[0] = nib_pair_to_half2(lo, hi, 0x0400);
+                v[1] = nib_pair_to_half2(lo, hi, 0x0501);
+                v[2] = nib_pair_to_half2(lo, hi, 0x0602);
+                v[3] = nib_pair_to_half2(lo, hi, 0x0703);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[i] = __hmul2(__hsub2(v[i], bias), s2);  // exact int, one rounding
+                *reinterpret_cast<uint4*>(out + off[u]) = *reinterpret_cast<uint4*>(v);
+            }
+        }
+    }
+}
+
+// Any even k, any group that divides k: one output element per thread.
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_dequant_int4_group_scalar(const uint8_t* __restrict__ wp, const __half* __restrict__ scales,
+                                  __half* __restrict__ out, int64_t n, int64_t k, int64_t group, int zp,
+                                  int64_t ldo) {
+    const int64_t total = n * k;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * kThreads) {
+        int64_t r = i / k, c = i - r * k;
+        uint32_t b = wp[r * (k / 2) + c / 2];
+        int q = (c & 1) ? (b >> 4) : (b & 15);
+        float s = __half2float(scales[r * (k / group) + c / group]);
+        out[r * ldo + c] = __float2half_rn(static_cast<float>(q - zp) * s);
+    }
+}
+
+namespace {
+// Exact int8 -> float without a convert instruction: place (b ^ 0x80) in the low mantissa byte of
+// 2^23, giving 2^23 + b + 128, then subtract 2^23 + 128.
+__device__ __forceinline__ float s8_to_float(uint32_t flipped, uint32_t byte_sel) {
+    uint32_t bits = __byte_perm(flipped, 0x4B000000u, 0x7540u | byte_sel);
+    return __uint_as_float(bits) - 8388736.0f;
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    if (BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&v);
+    } else {
+        __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+}
+}  // namespace
+
+// out[r, c] = cast((float(w) * scale[r]) [* post]);  one thread-chunk = 8 int8 = 16 output bytes.
+template <bool BF16, bool POST>
+__device__ __forceinline__ void dequant_int8_rowwise_body(const uint2* __restrict__ w, const float* __restrict__ scale,
+                                                          uint4* __restrict__ out, uint32_t chunks_per_row,
+                                                          uint64_t total_chunks, float post) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+    for (uint64_t base = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; base < total_chunks;
+         base += stride * kUnroll) {
+        uint2 raw[kUnroll];
+        float sc[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            uint64_t c = base + u * stride;
+            if (c < total_chunks) {
+                raw[u] = __ldg(w + c);
+                sc[u] = __ldg(scale + c / chunks_per_row);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            uint64_t c = base + u * stride;
+            if (c < total_chunks) {
+                const uint32_t x0 = raw[u].x ^ 0x80808080u, x1 = raw[u].y ^ 0x80808080u;
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    f[i] = s8_to_float(x0, i);
+                    f[4 + i] = s8_to_float(x1, i);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    f[i] = __fmul_rn(f[i], sc[u]);              // first fp32 rounding
+                    if (POST) f[i] = __fmul_rn(f[i], post);     // second fp32 rounding (reference order)
+                }
+                uint4 o;
+                o.x = pack2<BF16>(f[0], f[1]);
+                o.y = pack2<BF16>(f[2], f[3]);
+                o.z = pack2<BF16>(f[4], f[5]);
+                o.w = pack2<BF16>(f[6], f[7]);
+                out[c] = o;
+            }
+        }
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_dequant_int8_rowwise_bf16(const uint2* w, const float* scale, uint4* out, uint32_t cpr, uint64_t total,
+                                  float post) {
+    dequant_int8_rowwise_body<true, false>(w, scale, out, cpr, total, post);
+}
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_dequant_int8_rowwise_f16(const uint2* w, const float* scale, uint4* out, uint32_t cpr, uint64_t total,
+                                 float post) {
+    dequant_int8_rowwise_body<false, false>(w, scale, out, cpr, total, post);
+}
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_dequant_int8_rowwise_bf16_post(const uint2* w, const float* scale, uint4* out, uint32_t cpr,
+                                       uint64_t total, float post) {
+    dequant_int8_rowwise_body<true, true>(w, scale, out, cpr, total, post);
+}
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_dequant_int8_rowwise_f16_post(const uint2* w, const float* scale, uint4* out, uint32_t cpr,
+                                      uint64_t total, float post) {
+    dequant_int8_rowwise_body<false, true>(w, scale, out, cpr, total, post);
+}
+
+// Any cols: one element per thread.
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_dequant_int8_rowwise_scalar(const int8_t* __restrict__ w, const float* __restrict__ scale, void* out,
+                                    int64_t rows, int64_t cols, int bf16, int use_post, float post) {
+    const int64_t total = rows * cols;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * kThreads) {
+        float v = __fmul_rn(static_cast<float>(w[i]), scale[i / cols]);
+        if (use_post) v = __fmul_rn(v, post);
+        if (bf16) reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
+        else      reinterpret_cast<__half*>(out)[i] = __float2half_rn(v);
+    }
+}
+
+// Y = X * S[i/T, j/T].  16-bit types: the fp32 product of two 11-bit (8-bit) significands is exact,
+// so multiply in fp32 and round once — identical to a correctly rounded native multiply.
+namespace {
+template <int DT> struct Vec16;  // 16-byte chunk traits
+template <> struct Vec16<TB200_DT_F32> {
+    static constexpr int kElems = 4;
+    __device__ static float load_scale(const void* s, uint64_t i) { return __ldg(reinterpret_cast<const float*>(s) + i); }
+    __device__ static uint4 mul(uint4 x, float s) {
+        float* f = reinterpret_cast<float*>(&x);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = __fmul_rn(f[i], s);
+        return x;
+    }
+};
+template <> struct Vec16<TB200_DT_F16> {
+    static constexpr int kElems = 8;
+    __device__ static float load_scale(const void* s, uint64_t i) {
+        return __half2float(__ldg(reinterpret_cast<const __half*>(s) + i));
+    }
+    __device__ static uint4 mul(uint4 x, float s) {
+        __half2* h = reinterpret_cast<__half2*>(&x);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __half22float2(h[i]);
+            h[i] = __floats2half2_rn(__fmul_rn(f.x, s), __fmul_rn(f.y, s));
+        }
+        return x;
+    }
+};
+template <> struct Vec16<TB200_DT_BF16> {
+    static constexpr int kElems = 8;
+    __device__ static float load_scale(const void* s, uint64_t i) {
+        return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(s) + i));
+    }
+    __device__ static uint4 mul(uint4 x, float s) {
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&x);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __bfloat1622float2(h[i]);
+            h[i] = __floats2bfloat162_rn(__fmul_rn(f.x, s), __fmul_rn(f.y, s));
+        }
+        return x;
+    }
+};
+
+template <int DT>
+__device__ __forceinline__ void weight_dequant_body(const uint4* __restrict__ x, const void* __restrict__ s,
+                                                    uint4* __restrict__ y, uint32_t chunks_per_row,
+                                                    uint32_t tile_chunks, uint32_t tile_rows, uint32_t s_cols,
+                                                    uint64_t total_chunks) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+    for (uint64_t base = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; base < total_chunks;
+         base += stride * kUnroll) {
+        uint4 raw[kUnroll];
+        float sc[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            uint64_t c = base + u * stride;
+            if (c < total_chunks) {
+                uint64_t row = c / chunks_per_row;
+                uint32_t cc = static_cast<uint32_t>(c - row * chunks_per_row);
+                raw[u] = __ldg(x + c);
+                sc[u] = Vec16<DT>::load_scale(s, (row / tile_rows) * s_cols + cc / tile_chunks);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            uint64_t c = base + u * stride;
+            if (c < total_chunks) y[c] = Vec16<DT>::mul(raw[u], sc[u]);
+        }
+    }
+}
+}  // namespace
+
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_weight_dequant_f32(const uint4* x, const void* s, uint4* y, uint32_t cpr, uint32_t tc, uint32_t tr,
+                           uint32_t sc, uint64_t total) {
+    weight_dequant_body<TB200_DT_F32>(x, s, y, cpr, tc, tr, sc, total);
+}
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_weight_dequant_f16(const uint4* x, const void* s, uint4* y, uint32_t cpr, uint32_t tc, uint32_t tr,
+                           uint32_t sc, uint64_t total) {
+    weight_dequant_body<TB200_DT_F16>(x, s, y, cpr, tc, tr, sc, total);
+}
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_weight_dequant_bf16(const uint4* x, const void* s, uint4* y, uint32_t cpr, uint32_t tc, uint32_t tr,
+                            uint32_t sc, uint64_t total) {
+    weight_dequant_body<TB200_DT_BF16>(x, s, y, cpr, tc, tr, sc, total);
+}
+
+// Any m, n, tile: one element per thread.
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_weight_dequant_scalar(const void* __restrict__ x, const void* __restrict__ s, void* __restrict__ y,
+                              int64_t m, int64_t n, int64_t tile, int64_t s_cols, int dtype) {
+    const int64_t total = m * n;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * kThreads) {
+        int64_t r = i / n, c = i - r * n;
+        int64_t si = (r / tile) * s_cols + c / tile;
+        if (dtype == TB200_DT_F32) {
+            reinterpret_cast<float*>(y)[i] =
+                __fmul_rn(reinterpret_cast<const float*>(x)[i], reinterpret_cast<const float*>(s)[si]);
+        } else if (dtype == TB200_DT_F16) {
+            float v = __fmul_rn(__half2float(reinterpret_cast<const __half*>(x)[i]),
+                                __half2float(reinterpret_cast<const __half*>(s)[si]));
+            reinterpret_cast<__half*>(y)[i] = __float2half_rn(v);
+        } else {
+            float v = __fmul_rn(__bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[i]),
+                                __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(s)[si]));
+            reinterpret_cast<__nv_bfloat16*>(y)[i] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------------------
+extern "C" int tb200_dequant_int4_group(const void* wp, const void* scales, void* out, int64_t n, int64_t k,
+                                        int64_t group, int zero_point, int64_t ldo, void* stream) {
+    clear_error();
+    if (!wp || !scales || !out) return fail(TB200_ERR_ARG, "dequant_int4_group: null pointer");
+    if (n < 0 || k < 0) return fail(TB200_ERR_ARG, "dequant_int4_group: negative size n=%lld k=%lld", (long long)n, (long long)k);
+    if (group <= 0 || (k % 2) != 0 || (k % group) != 0)
+        return fail(TB200_ERR_ARG, "dequant_int4_group: k=%lld must be even and a multiple of group=%lld", (long long)k, (long long)group);
+    if (zero_point < 0 || zero_point > 15) return fail(TB200_ERR_ARG, "dequant_int4_group: zero_point %d outside 0..15", zero_point);
+    if (ldo < k) return fail(TB200_ERR_ARG, "dequant_int4_group: ldo=%lld < k=%lld", (long long)ldo, (long long)k);
+    if (n == 0 || k == 0) return TB200_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool vec = (group % 8 == 0) && (ldo % 8 == 0) && aligned16(out) &&
+                     ((reinterpret_cast<uintptr_t>(wp) & 3u) == 0) && (k / 8 < (1ll << 32));
+    if (vec) {
+        uint64_t total = static_cast<uint64_t>(n) * static_cast<uint64_t>(k / 8);
+        unsigned grid = grid_for(total, kThreads, kUnroll);
+        tb200_k_dequant_int4_group<<<grid, kThreads, 0, st>>>(
+            static_cast<const uint32_t*>(wp), static_cast<const __half*>(scales), static_cast<__half*>(out),
+            static_cast<uint32_t>(k / 8), static_cast<uint32_t>(group / 8), static_cast<uint32_t>(k / group), total,
+            ldo, 1024.0f + static_cast<float>(zero_point));
+    } else {
+        unsigned grid = grid_for(static_cast<uint64_t>(n) * k, kThreads, 1);
+        tb200_k_dequant_int4_group_scalar<<<grid, kThreads, 0, st>>>(
+            static_cast<const uint8_t*>(wp), static_cast<const __half*>(scales), static_cast<__half*>(out), n, k,
+            group, zero_point, ldo);
+    }
+    TB200_CUDA_TRY(cudaGetLastError());
+    return TB200_OK;
+}
+
+extern "C" int tb200_dequant_int8_rowwise(const void* w, const float* scale, void* out, int64_t rows, int64_t cols,
+                                          int out_dtype, int use_post, float post, void* stream) {
+    clear_error();
+    if (!w || !scale || !out) return fail(TB200_ERR_ARG, "dequant_int8_rowwise: null pointer");
+    if (rows < 0 || cols < 0) return fail(TB200_ERR_ARG, "dequant_int8_rowwise: negative size");
+    if (out_dtype != TB200_DT_F16 && out_dtype != TB200_DT_BF16)
+        return fail(TB200_ERR_UNSUPPORTED, "dequant_int8_rowwise: out_dtype %d (want F16 or BF16)", out_dtype);
+    if (rows == 0 || cols == 0) return TB200_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool bf16 = out_dtype == TB200_DT_BF16;
+    const bool vec = (cols % 8 == 0) && aligned16(out) && ((reinterpret_cast<uintptr_t>(w) & 7u) == 0) &&
+                     (cols / 8 < (1ll << 32));
+    if (vec) {
+        uint64_t total = static_cast<uint64_t>(rows) * static_cast<uint64_t>(cols / 8);
+        unsigned grid = grid_for(total, kThreads, kUnroll);
+        auto kern = bf16 ? (use_post ? tb200_k_dequant_int8_rowwise_bf16_post : tb200_k_dequant_int8_rowwise_bf16)
+                         : (use_post ? tb200_k_dequant_int8_rowwise_f16_post : tb200_k_dequant_int8_rowwise_f16);
+        kern<<<grid, kThreads, 0, st>>>(static_cast<const uint2*>(w), scale, static_cast<uint4*>(out),
+                                        static_cast<uint32_t>(cols / 8), total, post);
+    } else {
+        unsigned grid = grid_for(static_cast<uint64_t>(rows) * cols, kThreads, 1);
+        tb200_k_dequant_int8_rowwise_scalar<<<grid, kThreads, 0, st>>>(static_cast<const int8_t*>(w), scale, out,
+                                                                       rows, cols, bf16 ? 1 : 0, use_post, post);
+    }
+    TB200_CUDA_TRY(cudaGetLastError());
+    return TB200_OK;
+}
+
+extern "C" int tb200_weight_dequant_block(const void* x, const void* s, void* y, int64_t m, int64_t n, int64_t tile,
+                                          int dtype, void* stream) {
+    clear_error();
+    if (!x || !s || !y) return fail(TB200_ERR_ARG, "weight_dequant_block: null pointer");
+    if (m < 0 || n < 0 || tile <= 0) return fail(TB200_ERR_ARG, "weight_dequant_block: bad size m=%lld n=%lld tile=%lld", (long long)m, (long long)n, (long long)tile);
+    if (dtype != TB200_DT_F32 && dtype != TB200_DT_F16 && dtype != TB200_DT_BF16)
+        return fail(TB200_ERR_UNSUPPORTED, "weight_dequant_block: dtype %d", dtype);
+    if (m == 0 || n == 0) return TB200_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t s_cols = (n + tile - 1) / tile;
+    const int elems = dtype == TB200_DT_F32 ? 4 : 8;
+    const bool vec = (n % elems == 0) && (tile % elems == 0) && aligned16(x) && aligned16(y) &&
+                     (n / elems < (1ll << 32)) && (tile < (1ll << 32)) && (s_cols < (1ll << 32));
+    if (vec) {
+        uint64_t total = static_cast<uint64_t>(m) * static_cast<uint64_t>(n / elems);
+        unsigned grid = grid_for(total, kThreads, kUnroll);
+        auto kern = dtype == TB200_DT_F32 ? tb200_k_weight_dequant_f32
+                    : dtype == TB200_DT_F16 ? tb200_k_weight_dequant_f16 : tb200_k_weight_dequant_bf16;
+        kern<<<grid, kThreads, 0, st>>>(static_cast<const uint4*>(x), s, static_cast<uint4*>(y),
+                                        static_cast<uint32_t>(n / elems), static_cast<uint32_t>(tile / elems),
+                                        static_cast<uint32_t>(tile), static_cast<uint32_t>(s_cols), total);
+    } else {
+        unsigned grid = grid_for(static_cast<uint64_t>(m) * n, kThreads, 1);
+        tb200_k_weight_dequant_scalar<<<grid, kThreads, 0, st>>>(x, s, y, m, n, tile, s_cols, dtype);
+    }
+    TB200_CUDA_TRY(cudaGetLastError());
+    return TB200_OK;
+}

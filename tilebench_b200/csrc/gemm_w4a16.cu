@@ -1,0 +1,413 @@
+// W4A16 dequant-fused GEMM for sm_100a:
+//   out[m, col_offset + n] = fp16( sum_k a[m,k] * fp16((q[n,k] - zp) * s[n, k/group]) ),  fp32 accumulate.
+//
+// The kernel computes the transposed product D^T[n, m] = W[n,:] . A[m,:] so that the *weights* are
+// the tensor-memory operand of tcgen05.mma: the convert warps unpack int4 to fp16 in registers and
+// write the fragments straight into TMEM with tcgen05.st — the dequantised tile never goes back
+// through shared memory.  Activations arrive by TMA as the 128-byte-swizzled shared-memory operand
+// with MMA-N = the activation-row tile MT (16 for decode-sized m, 128 for large m).
+//
+// One persistent CTA per SM walks work items (weight tile, activation tile, K split).  Warp roles:
+//   warp 0            TMA producer: per 64-wide K block one [MT x 64] fp16 activation box and one
+//                     [128 x 32 B] packed-weight box (32-byte swizzle) into a shared-memory stage
+//   warp 1            MMA issuer: four tcgen05.mma kind::f16 (A from TMEM, B from smem, K = 16 each)
+//   warps 2..         convert warps (DQ groups of 4): thread = weight row; 2 x LDS.128 of packed
+//                     nibbles -> 64 fp16 -> tcgen05.st into one of AST operand stages in TMEM
+//   last 4 warps      epilogue: tcgen05.ld the finished accumulator (two buffers), cast, store
+// With a K split > 1 the epilogue writes fp32 partials to the caller's workspace and a second
+// kernel sums them in a fixed order (deterministic).  Every wait is bounded (see common.cuh).
+#include "common.cuh"
+
+namespace tb200 {
+namespace {
+
+constexpr int kBNW = 128;      // weight rows per tile (MMA M)
+constexpr int kBK = 64;        // K per stage: 64 fp16 = one 128-byte swizzle row
+constexpr int kWBytes = kBNW * (kBK / 2);   // 4096 packed bytes per stage
+constexpr int kGroupN = 16;    // tile-order grouping for L2 reuse
+
+template <int MT> struct W4Cfg {
+    static constexpr int kDQ = MT <= 32 ? 2 : 1;                 // convert warp groups
+    static constexpr int kActBytes = MT * kBK * 2;
+    static constexpr int kStageBytes = kActBytes + kWBytes;
+    static constexpr int kStages = MT <= 32 ? 16 : (MT == 64 ? 12 : 8);
+    static constexpr int kAStages = MT <= 32 ? 8 : 4;            // TMEM operand stages, 32 columns each
+    static constexpr int kDCols = 2 * MT;                        // two accumulator buffers
+    static constexpr int kACol0 = kDCols;
+    static constexpr int kTmemNeed = kDCols + 32 * kAStages;
+    static constexpr int kTmemCols = kTmemNeed <= 32 ? 32 : kTmemNeed <= 64 ? 64 : kTmemNeed <= 128 ? 128
+                                     : kTmemNeed <= 256 ? 256 : 512;
+    static constexpr int kWarps = 2 + 4 * kDQ + 4;
+    static constexpr int kThreads = 32 * kWarps;
+    static constexpr int kEpiWarp0 = 2 + 4 * kDQ;
+    static constexpr int kBarBytes = 512;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;
+};
+
+struct Item { int n_blk, m_blk, kb0, kb1, ks; };
+__device__ __forceinline__ Item make_item(int w, int tiles_n, int tiles_m, int splitk, int KB) {
+    const int tile = w / splitk;
+    const int ks = w - tile * splitk;
+    const int per_group = kGroupN * tiles_m;
+    const int g = tile / per_group;
+    const int first_n = g * kGroupN;
+    const int gsz = min(kGroupN, tiles_n - first_n);
+    const int r = tile - g * per_group;
+    Item it;
+    it.n_blk = first_n + r % gsz;
+    it.m_blk = r / gsz;
+    it.ks = ks;
+    it.kb0 = static_cast<int>(static_cast<int64_t>(ks) * KB / splitk);
+    it.kb1 = static_cast<int>(static_cast<int64_t>(ks + 1) * KB / splitk);
+    return it;
+}
+
+// (1024 + q) pairs -> fp16((q - zp) * s), exactly rounded once.
+__device__ __forceinline__ uint32_t dq_pair(uint32_t lo, uint32_t hi, uint32_t sel, __half2 bias, __half2 s2) {
+    uint32_t w = __byte_perm(lo, hi, sel);
+    uint32_t h;
+    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(h) : "r"(w));
+    __half2 v = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&h), bias), s2);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+}  // namespace
+}  // namespace tb200
+
+using namespace tb200;
+
+template <int MT>
+__device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ tmap_act, const CUtensorMap* __restrict__ tmap_w,
+                                                const __half* __restrict__ scales, __half* __restrict__ out,
+                                                float* __restrict__ ws, int M, int N, int K, int groups_per_row,
+                                                int kb_per_group, int64_t ldo, int64_t col_offset, int splitk,
+                                                float zp_plus_1024) {
+    using Cfg = W4Cfg<MT>;
+    constexpr int S = Cfg::kStages;
+    constexpr int AST = Cfg::kAStages;
+    constexpr int DQ = Cfg::kDQ;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);   // TMA landed
+    uint64_t* bar_empty = bar_full + S;                                              // MMA done with the stage
+    uint64_t* bar_afull = bar_empty + S;                                             // operand stage written
+    uint64_t* bar_aempty = bar_afull + AST;                                          // operand stage consumed
+    uint64_t* bar_dfull = bar_aempty + AST;                                          // accumulator complete
+    uint64_t* bar_dempty = bar_dfull + 2;                                            // accumulator drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_dempty + 2);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int KB = K / kBK;
+    const int tiles_n = N / kBNW;
+    const int tiles_m = (M + MT - 1) / MT;
+    const int items = tiles_n * tiles_m * splitk;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_empty[s], 1);
+        }
+        for (int s = 0; s < AST; ++s) {
+            mbar_init(&bar_afull[s], 128);
+            mbar_init(&bar_aempty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&bar_dfull[b], 1);
+            mbar_init(&bar_dempty[b], 128);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(tmap_act);
+        tma_prefetch_desc(tmap_w);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+                const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
+                for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
+                    const int s = it % S;
+                    if (!mbar_wait(&bar_empty[s], ((it / S) & 1) ^ 1, ST_WAIT_SMEM_EMPTY, kb)) { ok = false; break; }
+                    uint8_t* stage = smem + s * Cfg::kStageBytes;
+                    mbar_expect_tx(&bar_full[s], Cfg::kStageBytes);
+                    tma_load_2d(stage, tmap_act, &bar_full[s], kb * kBK, im.m_blk * MT);
+                    tma_load_2d(stage + Cfg::kActBytes, tmap_w, &bar_full[s], kb * (kBK / 2), im.n_blk * kBNW);
+                }
+            }
+            if (!ok) {
+                for (int s = 0; s < S; ++s) {
+                    if (it > static_cast<uint32_t>(s)) {
+                        uint32_t last = it - 1 - ((it - 1 - s) % S);
+                        (void)mbar_wait(&bar_full[s], (last / S) & 1, ST_WAIT_SMEM_FULL, -1);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(0, 0, kBNW, MT);   // f16 x f16 -> f32, M = 128, N = MT
+            uint32_t it = 0, item_cnt = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++item_cnt) {
+                const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
+                const int dbuf = item_cnt & 1;
+                if (!mbar_wait(&bar_dempty[dbuf], ((item_cnt >> 1) & 1) ^ 1, ST_WAIT_TMEM_EMPTY, w)) { ok = false; break; }
+                const uint32_t d_tmem = tmem_base + dbuf * MT;
+                for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
+                    const int s = it % S;
+                    const int as = it % AST;
+                    if (!mbar_wait(&bar_full[s], (it / S) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
+                    if (!mbar_wait(&bar_afull[as], (it / AST) & 1, ST_WAIT_OPERAND, kb)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t b_desc = umma_desc_sw128(smem_u32(smem + s * Cfg::kStageBytes));
+                    const uint32_t a_tmem = tmem_base + Cfg::kACol0 + as * 32;
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k) {
+                        // 16 fp16 of K = 8 TMEM columns of the operand, 32 bytes of the swizzled smem row
+                        umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, (kb > im.kb0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&bar_empty[s]);
+                    tc_commit(&bar_aempty[as]);
+                }
+                if (ok) tc_commit(&bar_dfull[dbuf]);
+            }
+        }
+    } else if (warp < Cfg::kEpiWarp0) {
+        // ---------------- convert warps: packed int4 (smem) -> fp16 operand (TMEM) ----------------
+        const int grp = (warp - 2) >> 2;                 // which K blocks this group takes (it % DQ == grp)
+        const int lane_grp = warp & 3;
+        const int row = lane_grp * 32 + lane;            // weight row inside the tile == TMEM lane
+        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + Cfg::kACol0;
+        const __half2 bias = __float2half2_rn(zp_plus_1024);
+        // physical offset of this row's two 16-byte chunks under the 32-byte TMA swizzle
+        const uint32_t swz = ((row >> 2) & 1) << 4;
+        const uint32_t off0 = row * 32 + (0u ^ swz), off1 = row * 32 + (16u ^ swz);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+            const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
+            const __half* srow = scales + static_cast<int64_t>(im.n_blk * kBNW + row) * groups_per_row;
+            for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
+                if (static_cast<int>(it % DQ) != grp) continue;
+                const int s = it % S;
+                const int as = it % AST;
+                const __half sc = __ldg(srow + kb / kb_per_group);
+                if (!mbar_wait(&bar_full[s], (it / S) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
+                const uint8_t* wt = smem + s * Cfg::kStageBytes + Cfg::kActBytes;
+                const uint4 p0 = *reinterpret_cast<const uint4*>(wt + off0);
+                const uint4 p1 = *reinterpret_cast<const uint4*>(wt + off1);
+                const __half2 s2 = __half2half2(sc);
+                uint32_t frag[32];
+                const uint32_t pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t lo = pw[i], hi = pw[i] >> 4;
+                    frag[4 * i + 0] = dq_pair(lo, hi, 0x0400, bias, s2);
+                    frag[4 * i + 1] = dq_pair(lo, hi, 0x0501, bias, s2);
+                    frag[4 * i + 2] = dq_pair(lo, hi, 0x0602, bias, s2);
+                    frag[4 * i + 3] = dq_pair(lo, hi, 0x0703, bias, s2);
+                }
+                if (!mbar_wait(&bar_aempty[as], ((it / AST) & 1) ^ 1, ST_WAIT_OPERAND, -kb - 1)) { ok = false; break; }
+                tc_fence_after();
+                tmem_st32(t_lane + as * 32, frag);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&bar_afull[as]);
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int lane_grp = warp & 3;
+        const int row = lane_grp * 32 + lane;
+        constexpr int kChunk = MT >= 32 ? 32 : 16;
+        uint32_t item_cnt = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++item_cnt) {
+            const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
+            const int dbuf = item_cnt & 1;
+            if (!mbar_wait(&bar_dfull[dbuf], (item_cnt >> 1) & 1, ST_WAIT_TMEM_FULL, w)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + dbuf * MT;
+            const int64_t n = static_cast<int64_t>(im.n_blk) * kBNW + row;
+#pragma unroll
+            for (int c = 0; c < MT / kChunk; ++c) {
+                uint32_t v[kChunk];
+                if constexpr (kChunk == 32) tmem_ld32(t_lane + c * kChunk, v);
+                else                        tmem_ld16(t_lane + c * kChunk, v);
+                tmem_wait_ld();
+                const int m0 = im.m_blk * MT + c * kChunk;
+                if (splitk == 1) {
+                    __half* dst = out + col_offset + n;
+#pragma unroll
+                    for (int j = 0; j < kChunk; ++j)
+                        if (m0 + j < M) dst[static_cast<int64_t>(m0 + j) * ldo] = __float2half_rn(__uint_as_float(v[j]));
+                } else {
+                    float* dst = ws + static_cast<int64_t>(im.ks) * M * N + n;
+#pragma unroll
+                    for (int j = 0; j < kChunk; ++j)
+                        if (m0 + j < M) dst[static_cast<int64_t>(m0 + j) * N] = __uint_as_float(v[j]);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&bar_dempty[dbuf]);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+#define TB200_W4_KERNEL(MT)                                                                                        \
+    extern "C" __global__ void __launch_bounds__(W4Cfg<MT>::kThreads, 1) tb200_k_gemm_w4a16_m##MT(                 \
+        const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_w,                  \
+        const __half* scales, __half* out, float* ws, int M, int N, int K, int gpr, int kbpg, int64_t ldo,         \
+        int64_t col_offset, int splitk, float zp1024) {                                                            \
+        gemm_w4a16_body<MT>(&tmap_act, &tmap_w, scales, out, ws, M, N, K, gpr, kbpg, ldo, col_offset, splitk,      \
+                            zp1024);                                                                               \
+    }
+TB200_W4_KERNEL(16)
+TB200_W4_KERNEL(64)
+TB200_W4_KERNEL(128)
+
+// out[m, col_offset + n] = fp16( ws[0][m][n] + ws[1][m][n] + ... ) — fixed order, 4 columns per thread.
+extern "C" __global__ void __launch_bounds__(256)
+tb200_k_splitk_reduce_f16(const float* __restrict__ ws, __half* __restrict__ out, int64_t M, int64_t N, int splitk,
+                          int64_t ldo, int64_t col_offset) {
+    const int64_t n4 = N / 4;
+    const int64_t total = M * n4;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * 256) {
+        const int64_t m = i / n4, c = (i - m * n4) * 4;
+        float4 acc = __ldg(reinterpret_cast<const float4*>(ws + m * N + c));
+        for (int s = 1; s < splitk; ++s) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(ws + (static_cast<int64_t>(s) * M + m) * N + c));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+        __half* dst = out + m * ldo + col_offset + c;
+        if ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+            uint2 o;
+            o.x = *reinterpret_cast<uint32_t*>(&lo);
+            o.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(dst) = o;
+        } else {
+            dst[0] = __low2half(lo); dst[1] = __high2half(lo); dst[2] = __low2half(hi); dst[3] = __high2half(hi);
+        }
+    }
+}
+
+TB200_DEFINE_STATUS_HOOKS(gemm_w4a16)
+
+namespace {
+
+int pick_mt(int64_t m) { return m <= 16 ? 16 : (m <= 64 ? 64 : 128); }
+
+// K split for the decode-sized shapes, where there are fewer weight tiles than SMs and the kernel
+// is bound by streaming the weights: pick the split that fills whole waves of SMs best.
+int pick_splitk(int64_t m, int64_t n, int64_t k) {
+    const int mt = pick_mt(m);
+    if (mt > 16) return 1;
+    const int64_t tiles = (n / kBNW) * ((m + mt - 1) / mt);
+    const int sms = num_sms();
+    const int64_t KB = k / kBK;
+    int best = 1;
+    double best_eff = 0.0;
+    for (int s = 1; s <= 16; ++s) {
+        if (KB / s < 4) break;
+        const int64_t items = tiles * s;
+        const int64_t waves = (items + sms - 1) / sms;
+        const double eff = static_cast<double>(items) / static_cast<double>(waves * sms);
+        if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    }
+    return best;
+}
+
+template <int MT, typename Kern>
+int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void* out, float* ws, int64_t m, int64_t n,
+              int64_t k, int64_t group, int zp, int64_t ldo, int64_t col_offset, int splitk, cudaStream_t st) {
+    using Cfg = W4Cfg<MT>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    TB200_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        TB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        attr_set[dev] = true;
+    }
+    CUtensorMap ta, tw;
+    int rc = encode_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, m, k, k * 2, MT, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TB200_OK) return rc;
+    rc = encode_tmap_2d(&tw, wp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k / 2, k / 2, kBNW, kBK / 2, CU_TENSOR_MAP_SWIZZLE_32B);
+    if (rc != TB200_OK) return rc;
+    const int64_t items = (n / kBNW) * ((m + MT - 1) / MT) * splitk;
+    const int grid = static_cast<int>(items < num_sms() ? items : num_sms());
+    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(ta, tw, static_cast<const __half*>(scales), static_cast<__half*>(out), ws,
+                                                        static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
+                                                        static_cast<int>(k / group), static_cast<int>(group / kBK), ldo,
+                                                        col_offset, splitk, 1024.0f + static_cast<float>(zp));
+    TB200_CUDA_TRY(cudaGetLastError());
+    if (splitk > 1) {
+        const int64_t total = m * (n / 4);
+        int64_t blocks = (total + 255) / 256;
+        const int64_t cap = static_cast<int64_t>(num_sms()) * 8;
+        if (blocks > cap) blocks = cap;
+        tb200_k_splitk_reduce_f16<<<static_cast<unsigned>(blocks), 256, 0, st>>>(ws, static_cast<__half*>(out), m, n, splitk, ldo,
+                                                                                 col_offset);
+        TB200_CUDA_TRY(cudaGetLastError());
+    }
+    return TB200_OK;
+}
+
+}  // namespace
+
+extern "C" size_t tb200_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+    if (m <= 0 || n <= 0 || k <= 0 || n % kBNW != 0 || k % 128 != 0) return 0;
+    const int s = pick_splitk(m, n, k);
+    return s > 1 ? static_cast<size_t>(s) * m * n * sizeof(float) : 0;
+}
+
+extern "C" int tb200_gemm_w4a16(const void* a, const void* wp, const void* scales, void* out, int64_t m, int64_t n,
+                                int64_t k, int64_t group, int zero_point, int64_t ldo, int64_t col_offset,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+    clear_error();
+    if (!a || !wp || !scales || !out) return fail(TB200_ERR_ARG, "gemm_w4a16: null pointer");
+    if (m <= 0 || n <= 0 || k <= 0) return fail(TB200_ERR_ARG, "gemm_w4a16: non-positive size m=%lld n=%lld k=%lld", (long long)m, (long long)n, (long long)k);
+    if (n % kBNW != 0) return fail(TB200_ERR_ARG, "gemm_w4a16: n=%lld must be a multiple of 128", (long long)n);
+    if (group <= 0 || group % kBK != 0 || k % group != 0 || k % 128 != 0)
+        return fail(TB200_ERR_ARG, "gemm_w4a16: k=%lld must be a multiple of 128 and of group=%lld, group a multiple of 64", (long long)k, (long long)group);
+    if (zero_point < 0 || zero_point > 15) return fail(TB200_ERR_ARG, "gemm_w4a16: zero_point %d outside 0..15", zero_point);
+    if (col_offset < 0 || ldo < col_offset + n) return fail(TB200_ERR_ARG, "gemm_w4a16: ldo=%lld < col_offset+n=%lld", (long long)ldo, (long long)(col_offset + n));
+    if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) return fail(TB200_ERR_UNSUPPORTED, "gemm_w4a16: dimension too large");
+    if (!aligned16(a) || !aligned16(wp)) return fail(TB200_ERR_ALIGN, "gemm_w4a16: a and wp must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int splitk = pick_splitk(m, n, k);
+    float* ws = nullptr;
+    if (splitk > 1) {
+        const size_t need = static_cast<size_t>(splitk) * m * n * sizeof(float);
+        if (!workspace || workspace_bytes < need)
+            return fail(TB200_ERR_WORKSPACE, "gemm_w4a16: needs %zu workspace bytes, got %zu", need, workspace ? workspace_bytes : 0);
+        if (!aligned16(workspace)) return fail(TB200_ERR_ALIGN, "gemm_w4a16: workspace must be 16-byte aligned");
+        ws = static_cast<float*>(workspace);
+    }
+    switch (pick_mt(m)) {
+        case 16:  return launch_w4<16>(tb200_k_gemm_w4a16_m16, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
+        case 64:  return launch_w4<64>(tb200_k_gemm_w4a16_m64, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
+        default:  return launch_w4<128>(tb200_k_gemm_w4a16_m128, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
+    }
+}

@@ -1,0 +1,174 @@
+"""Seeded input generators and the case grid.
+
+The reference generates unseeded tensors on the device (tilebench/data/tensors.py:11, :179-184,
+:416-448, :492-499).  Parity on identical inputs needs a seed, so every generator here draws on
+the CPU from an explicit torch.Generator and then moves the tensors to `device`; the same CPU
+tensors feed the oracle.  `expand_cases` / `infer_problem_size` / `GENERATORS` keep the
+reference's surface (tensors.py:26-39, :560-627, :630-785).
+"""
+from __future__ import annotations
+
+import math
+from itertools import product
+
+import torch
+
+DEFAULT_DEVICE = "cuda" if torch.cuda.is_available() else "cpu"
+#: Base seed; a case's seed is SEED0 + 1000 * operator index + case index unless given.
+SEED0 = 20261125
+
+FP8_MAX = 448.0
+
+
+def _gen(seed: int) -> torch.Generator:
+    return torch.Generator(device="cpu").manual_seed(int(seed))
+
+
+def _normalize_sequence(values, name):
+    if isinstance(values, dict) and "expr" in values:
+        result = eval(values["expr"])  # noqa: S307  (package-internal configs only)
+        if not isinstance(result, (list, tuple)) or len(result) == 0:
+            raise ValueError(f"case_grid expr for '{name}' must evaluate to a non-empty list.")
+        return list(result)
+    if not isinstance(values, (list, tuple)) or len(values) == 0:
+        raise ValueError(f"case_grid field '{name}' must be a non-empty list/tuple.")
+    return list(values)
+
+
+def _expand_case_grid(case_grid, case_defaults=None):
+    if not isinstance(case_grid, dict) or len(case_grid) == 0:
+        raise ValueError("case_grid must be a non-empty mapping of parameter -> candidate list.")
+    keys = list(case_grid)
+    lists = [_normalize_sequence(case_grid[k], k) for k in keys]
+    cases = []
+    for combo in product(*lists):
+        case = dict(case_defaults or {})
+        case.update(zip(keys, combo))
+        cases.append(case)
+    return cases
+
+
+def expand_cases(operator_name, config):
+    """Priority: explicit test_cases, then case_grid over case_defaults."""
+    if config.get("test_cases"):
+        return list(config["test_cases"])
+    if "case_grid" in config:
+        return _expand_case_grid(config["case_grid"], config.get("case_defaults", {}))
+    raise ValueError(f"Operator '{operator_name}' config must define test_cases or case_grid.")
+
+
+# ---- quantised-weight inputs ------------------------------------------------------------------
+
+def make_int4_group_weights(N, K, GROUP=128, seed=SEED0):
+    """Packed uint8 [N, K/2] (each nibble uniform 0..15, low nibble = even k) and fp16 scales
+    [N, K/GROUP] drawn as |N(0,1)| * 0.01 + 1e-3."""
+    g = _gen(seed)
+    wp = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g)
+    scales = (torch.randn(N, K // GROUP, generator=g).abs() * 0.01 + 1e-3).to(torch.float16)
+    return wp, scales
+
+
+def generate_dequant_int4_group_inputs(N, K, GROUP=128, ZP=8, dtype=torch.float16, device=DEFAULT_DEVICE,
+                                       seed=SEED0, **kwargs):
+    wp, scales = make_int4_group_weights(N, K, GROUP, seed)
+    return (wp.to(device), scales.to(device), GROUP, ZP)
+
+
+def generate_dequant_int8_channel_inputs(rows, cols, dtype=torch.bfloat16, device=DEFAULT_DEVICE,
+                                         seed=SEED0 + 1000, **kwargs):
+    g = _gen(seed)
+    w = torch.randint(-127, 128, (rows, cols), dtype=torch.int8, generator=g)
+    scale = torch.randn(rows, generator=g).abs() * 0.02 + 1e-4
+    return (w.to(device), scale.to(device))
+
+
+def generate_gemm_w4a16_inputs(M, K, N, GROUP=128, ZP=8, dtype=torch.float16, device=DEFAULT_DEVICE,
+                               seed=SEED0 + 2000, **kwargs):
+    g = _gen(seed)
+    a = torch.randn(M, K, generator=g).to(torch.float16)
+    wp, scales = make_int4_group_weights(N, K, GROUP, seed + 1)
+    return (a.to(device), wp.to(device), scales.to(device), GROUP, ZP)
+
+
+def quantize_fp8_blockwise(x: torch.Tensor, block_rows: int, block_cols: int = 128):
+    """e4m3 quantisation with one fp32 scale = amax/448 per [block_rows x block_cols] block
+    (scale 1 for an all-zero block).  Returns (q, scales[rows/block_rows, cols/block_cols])."""
+    R, C = x.shape
+    xb = x.reshape(R // block_rows, block_rows, C // block_cols, block_cols)
+    amax = xb.abs().amax(dim=(1, 3))
+    scale = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax)).to(torch.float32)
+    q = (xb / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).reshape(R, C).to(torch.float8_e4m3fn)
+    return q, scale
+
+
+def generate_gemm_fp8_blockscaled_inputs(S=None, BLOCK=128, M=None, N=None, K=None, dtype=torch.float8_e4m3fn,
+                                         device=DEFAULT_DEVICE, seed=SEED0 + 3000, **kwargs):
+    M = M or S
+    N = N or S
+    K = K or S
+    g = _gen(seed)
+    a = torch.randn(M, K, generator=g)
+    b = torch.randn(N, K, generator=g)
+    aq, sa = quantize_fp8_blockwise(a, 1, BLOCK)
+    bq, sb = quantize_fp8_blockwise(b, BLOCK, BLOCK)
+    return (aq.to(device), sa.to(device), bq.to(device), sb.to(device))
+
+
+def generate_gemm_w4a16_npart_inputs(M, K, N, WORLD=1, GATHER=1, GROUP=128, ZP=8, dtype=torch.float16,
+                                     device=DEFAULT_DEVICE, seed=SEED0 + 4000, **kwargs):
+    a, wp, scales, group, zp = generate_gemm_w4a16_inputs(M, K, N, GROUP, ZP, device=device, seed=seed)
+    return (a, wp, scales, group, zp, WORLD, GATHER)
+
+
+# ---- the reference's own operators (seeded versions of tensors.py:179-184 and :492-499) -------
+
+def generate_dequantize_rowwise_inputs(rows, cols, device=DEFAULT_DEVICE, seed=SEED0 + 5000, **kwargs):
+    g = _gen(seed)
+    x = torch.randint(-128, 127, (rows, cols), dtype=torch.int8, generator=g)
+    state_x = torch.rand(rows, dtype=torch.float32, generator=g) * 10.0
+    return (x.to(device), state_x.to(device))
+
+
+def generate_weight_dequant_inputs(M, TILE_SIZE, dtype, N=None, device=DEFAULT_DEVICE, seed=SEED0 + 6000, **kwargs):
+    if N is None:
+        N = M
+    g = _gen(seed)
+    X = torch.randn(M, N, generator=g).to(dtype)
+    S = torch.randn(math.ceil(M / TILE_SIZE), math.ceil(N / TILE_SIZE), generator=g).to(dtype)
+    return (X.to(device), S.to(device), M, N, TILE_SIZE)
+
+
+GENERATORS = {
+    "dequant_int4_group": generate_dequant_int4_group_inputs,
+    "dequant_int8_channel": generate_dequant_int8_channel_inputs,
+    "gemm_w4a16": generate_gemm_w4a16_inputs,
+    "gemm_fp8_blockscaled": generate_gemm_fp8_blockscaled_inputs,
+    "gemm_w4a16_npart": generate_gemm_w4a16_npart_inputs,
+    "dequantize_rowwise": generate_dequantize_rowwise_inputs,
+    "weight_dequant": generate_weight_dequant_inputs,
+}
+
+
+def get_generator(operator_name):
+    if operator_name not in GENERATORS:
+        raise ValueError(f"Unsupported operator '{operator_name}'. Available operators: {list(GENERATORS)}")
+    return GENERATORS[operator_name]
+
+
+def infer_problem_size(operator_name, params):
+    """Element count of the case's main output; the x axis of size plots."""
+    if "n" in params:
+        return int(params["n"])
+    p = params
+    if operator_name == "dequant_int4_group":
+        return int(p["N"]) * int(p["K"])
+    if operator_name in ("dequant_int8_channel", "dequantize_rowwise"):
+        return int(p["rows"]) * int(p["cols"])
+    if operator_name in ("gemm_w4a16", "gemm_w4a16_npart"):
+        return int(p["M"]) * int(p["N"])
+    if operator_name == "gemm_fp8_blockscaled":
+        s = int(p.get("S") or 0)
+        return int(p.get("M") or s) * int(p.get("N") or s)
+    if operator_name == "weight_dequant":
+        return int(p["M"]) * int(p.get("N") or p["M"])
+    return 1
