@@ -120,6 +120,30 @@ int    tb200_gemm_w4a16(const void* a, const void* wp, const void* scales, void*
                         int64_t ldo, int64_t col_offset,
                         void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * W4A16 GEMM for callers that cannot allocate device memory.  No counterpart in the reference.
+ *
+ * tb200_gemm_w4a16 asks its caller for a split-K workspace when m is decode-sized.  Some callers have
+ * no way to provide one: a plugin running inside a host process that has handed all device memory to its
+ * own pool, or code invoked where cudaMalloc is not permitted.  This variant computes the same result
+ * with the partial sums kept in a fixed array of TB200_W4A16_STATIC_SCRATCH_BYTES that is part of the
+ * library image (every GPU that loads the library holds that much memory until the process exits).  It
+ * calls no cudaMalloc / cudaFree and no allocating library routine; inputs and the output are still the
+ * caller's buffers.
+ *   - Shapes whose split-K partials exceed the array are rejected with TB200_ERR_WORKSPACE and a message
+ *     giving both sizes; shapes that need no scratch (large m) run exactly like tb200_gemm_w4a16.
+ *   - The first call on each device resolves the array's device address (cudaGetSymbolAddress, with that
+ *     device current).  Make that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  Every
+ *     partial sum a call reads is written by that same call first, so nothing has to be cleared; but two
+ *     calls that overlap on the GPU (different streams, or concurrent graphs) race on it.  Serialise them.
+ */
+#define TB200_W4A16_STATIC_SCRATCH_BYTES (8u << 20)
+size_t tb200_gemm_w4a16_static_scratch_bytes(void);
+int    tb200_gemm_w4a16_static(const void* a, const void* wp, const void* scales, void* out,
+                               int64_t m, int64_t n, int64_t k, int64_t group, int zero_point,
+                               int64_t ldo, int64_t col_offset, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Device status word.  Every wait inside the GEMM kernels (mbarrier, TMEM hand-off) is bounded;
  * a wait that runs out records a code here and the kernel drains and returns instead of hanging.

@@ -18,6 +18,8 @@
 // kernel sums them in a fixed order (deterministic).  Every wait is bounded (see common.cuh).
 #include "common.cuh"
 
+#include <mutex>
+
 namespace tb200 {
 namespace {
 
@@ -410,4 +412,51 @@ extern "C" int tb200_gemm_w4a16(const void* a, const void* wp, const void* scale
         case 64:  return launch_w4<64>(tb200_k_gemm_w4a16_m64, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
         default:  return launch_w4<128>(tb200_k_gemm_w4a16_m128, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant: the split-K partial sums live in a fixed array inside the library image.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr size_t kStaticScratchBytes = TB200_W4A16_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) float g_w4a16_scratch[kStaticScratchBytes / sizeof(float)];
+
+// Device address of g_w4a16_scratch, resolved once per device.  In host code the array's name is
+// only a handle for the runtime; the pointer a kernel can use comes from cudaGetSymbolAddress.
+int static_scratch_ptr(float** out) {
+    static float* cached[64] = {nullptr};
+    static std::mutex mu;
+    int dev = 0;
+    TB200_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(TB200_ERR_UNSUPPORTED, "gemm_w4a16_static: device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_w4a16_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_w4a16_scratch)");
+        cached[dev] = static_cast<float*>(p);
+    }
+    *out = cached[dev];
+    return TB200_OK;
+}
+}  // namespace
+
+extern "C" size_t tb200_gemm_w4a16_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int tb200_gemm_w4a16_static(const void* a, const void* wp, const void* scales, void* out, int64_t m,
+                                       int64_t n, int64_t k, int64_t group, int zero_point, int64_t ldo,
+                                       int64_t col_offset, void* stream) {
+    clear_error();
+    const size_t need = tb200_gemm_w4a16_workspace_bytes(m, n, k);
+    if (need > kStaticScratchBytes)
+        return fail(TB200_ERR_WORKSPACE,
+                    "gemm_w4a16_static: m=%lld n=%lld k=%lld needs %zu scratch bytes, the built-in array holds %zu; "
+                    "use tb200_gemm_w4a16 with a caller workspace",
+                    (long long)m, (long long)n, (long long)k, need, kStaticScratchBytes);
+    float* ws = nullptr;
+    if (need > 0) {
+        int rc = static_scratch_ptr(&ws);
+        if (rc != TB200_OK) return rc;
+    }
+    return tb200_gemm_w4a16(a, wp, scales, out, m, n, k, group, zero_point, ldo, col_offset, ws, need, stream);
 }
