@@ -114,25 +114,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: polls until the phase completes or kWaitNs of wall time (the GPU's nanosecond
-// timer) have passed, far longer than any legitimate wait here (a whole kernel runs in
-// milliseconds).  On expiry it records `code` and returns false; the caller unwinds and exits.
-constexpr uint64_t kWaitNs = 2000000000ull;
-__device__ __forceinline__ uint64_t global_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+// Bounded wait: polls until the phase completes or kWaitCycles SM clock cycles have passed (about
+// two seconds — far longer than any legitimate wait here, a whole kernel runs in milliseconds).
+// The bound uses the SM-local cycle counter: reading it costs a few cycles, unlike the global
+// nanosecond timer.  On expiry it records `code` and returns false; the caller unwinds and exits.
+constexpr long long kWaitCycles = 1ll << 32;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code, int detail) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 32; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-    }
-    const uint64_t t0 = global_ns();
-#pragma unroll 1
-    for (uint32_t i = 0;; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 15u) == 15u && global_ns() - t0 > kWaitNs) break;
+        for (int i = 0; i < 128; ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (clock64() - t0 > kWaitCycles) break;
     }
     record_status(code, detail);
     return false;

@@ -26,7 +26,12 @@ template <int BN> struct Fp8Cfg {
     static constexpr int kBBytes = BN * kBK;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kDrainWarps = 4 * (BN / 128);
-    static constexpr int kThreads = 64 + 32 * kDrainWarps;
+    static constexpr int kCtrlWarps = 4;                        // warp 0 TMA, warp 1 MMA, 2 idle: one warpgroup
+    static constexpr int kThreads = 32 * (kCtrlWarps + kDrainWarps);
+    // 384-thread CTAs start at 168 registers per thread; the control warpgroup gives most of its
+    // share back and the drain warpgroups take it (setmaxnreg), so 128 running sums plus 64
+    // in-flight TMEM values fit without spilling.  The 256-thread variant has room as launched.
+    static constexpr bool kReallocRegs = BN == 256;
     static constexpr int kTmemCols = 2 * BN;                    // two accumulator buffers
     static constexpr int kBarBytes = 256;
     static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
@@ -53,14 +58,11 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
                                               __nv_bfloat16* __restrict__ out, int M, int N, int K, int64_t ldo) {
     using Cfg = Fp8Cfg<BN>;
     constexpr int S = Cfg::kStages;
-    // columns fetched per tcgen05.ld: 16 keeps the 10-warp CTA inside its 168-register budget
-    constexpr int kDrainChunk = BN == 256 ? 16 : 32;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
     uint64_t* bar_empty = bar_full + S;
-    uint64_t* bar_tfull = bar_empty + S;
-    uint64_t* bar_tempty = bar_tfull + 2;
+    uint64_t* bar_tempty = bar_empty + S;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
 
     const int warp = threadIdx.x >> 5;
@@ -76,8 +78,7 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
             mbar_init(&bar_empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(&bar_tfull[b], 1);
-            mbar_init(&bar_tempty[b], 32 * Cfg::kDrainWarps);
+            mbar_init(&bar_tempty[b], Cfg::kDrainWarps);   // one arrival per drain warp
         }
         mbar_fence_init();
         tma_prefetch_desc(tmap_a);
@@ -92,7 +93,9 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0) {
+    if (warp < Cfg::kCtrlWarps) {
+      if constexpr (Cfg::kReallocRegs) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+      if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t it = 0;
@@ -141,14 +144,17 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
                         // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte units
                         umma_f8_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
                     }
-                    tc_commit(&bar_empty[s]);     // stage reusable once these MMAs have read it
-                    tc_commit(&bar_tfull[buf]);   // accumulator complete
+                    // one commit per K block: "MMAs of this block are complete" both frees the smem
+                    // stage for the producer and tells the drain warps the accumulator is ready
+                    tc_commit(&bar_empty[s]);
                 }
             }
         }
+      }
     } else {
+        if constexpr (Cfg::kReallocRegs) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
         // ---------------- drain warps ----------------
-        const int dw = warp - 2;
+        const int dw = warp - Cfg::kCtrlWarps;
         const int lane_grp = warp & 3;             // TMEM lanes this warp may read: 32*(warp%4)..+31
         const int half = dw >> 2;                  // which 128-column half of the tile
         const int row_in_tile = lane_grp * 32 + lane;
@@ -162,9 +168,9 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
             const bool row_ok = m < M;
             const float* sa_row = sa + static_cast<int64_t>(row_ok ? m : 0) * KBs;
             const float* sb_row = sb + static_cast<int64_t>(tc.n_blk * (BN / 128) + half) * KBs;
-            float acc[128];
+            uint64_t acc2[64];                               // 128 running sums as packed f32 pairs
 #pragma unroll
-            for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+            for (int j = 0; j < 64; ++j) acc2[j] = 0ull;
             // scales are prefetched two K blocks ahead of their use
             float sc0 = __ldg(sa_row) * __ldg(sb_row);
             float sc1 = KB > 1 ? __ldg(sa_row + 1) * __ldg(sb_row + 1) : 0.f;
@@ -172,23 +178,45 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
                 const int buf = it & 1;
                 float sc2 = 0.f;
                 if (kb + 2 < KB) sc2 = __ldg(sa_row + kb + 2) * __ldg(sb_row + kb + 2);
-                if (!mbar_wait(&bar_tfull[buf], (it >> 1) & 1, ST_WAIT_TMEM_FULL, kb)) { ok = false; break; }
+                if (!mbar_wait(&bar_empty[it % S], (it / S) & 1, ST_WAIT_TMEM_FULL, kb)) { ok = false; break; }
                 tc_fence_after();
-                const float scale = sc0;
+                uint64_t scale2;
+                asm("mov.b64 %0, {%1, %1};" : "=l"(scale2) : "f"(sc0));
 #pragma unroll
-                for (int c = 0; c < 128 / kDrainChunk; ++c) {
-                    uint32_t v[kDrainChunk];
-                    if constexpr (kDrainChunk == 32) tmem_ld32(t_lane + buf * BN + c * kDrainChunk, v);
-                    else                             tmem_ld16(t_lane + buf * BN + c * kDrainChunk, v);
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t v0[32], v1[32];
+                    tmem_ld32(t_lane + buf * BN + c * 64, v0);
+                    tmem_ld32(t_lane + buf * BN + c * 64 + 32, v1);
                     tmem_wait_ld();
+                    if (c == 1) {                            // everything is in registers: free the buffer now
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bar_tempty[buf]);
+                    }
 #pragma unroll
-                    for (int j = 0; j < kDrainChunk; ++j)
-                        acc[c * kDrainChunk + j] = fmaf(__uint_as_float(v[j]), scale, acc[c * kDrainChunk + j]);
+                    for (int j = 0; j < 16; ++j) {
+                        uint64_t p;
+                        asm("mov.b64 %0, {%1, %2};" : "=l"(p) : "r"(v0[2 * j]), "r"(v0[2 * j + 1]));
+                        asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc2[c * 32 + j]) : "l"(p), "l"(scale2));
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        uint64_t p;
+                        asm("mov.b64 %0, {%1, %2};" : "=l"(p) : "r"(v1[2 * j]), "r"(v1[2 * j + 1]));
+                        asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc2[c * 32 + 16 + j]) : "l"(p), "l"(scale2));
+                    }
                 }
-                tc_fence_before();
-                mbar_arrive(&bar_tempty[buf]);
                 sc0 = sc1;
                 sc1 = sc2;
+            }
+            float acc[128];
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+                uint32_t lo, hi;
+                asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(acc2[j]));
+                acc[2 * j] = __uint_as_float(lo);
+                acc[2 * j + 1] = __uint_as_float(hi);
             }
             if (ok && row_ok) {
                 __nv_bfloat16* dst = out + static_cast<int64_t>(m) * ldo + tc.n_blk * BN + half * 128;

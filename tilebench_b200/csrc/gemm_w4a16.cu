@@ -5,15 +5,19 @@
 // the tensor-memory operand of tcgen05.mma: the convert warps unpack int4 to fp16 in registers and
 // write the fragments straight into TMEM with tcgen05.st — the dequantised tile never goes back
 // through shared memory.  Activations arrive by TMA as the 128-byte-swizzled shared-memory operand
-// with MMA-N = the activation-row tile MT (16 for decode-sized m, 128 for large m).
+// with MMA-N = the activation-row tile MT (16 for decode-sized m, 64, or 128).  For m > 128 one
+// work item covers TWO 128-row activation tiles that share every converted weight stage (two
+// accumulators), which halves the convert and hand-off work per flop.
 //
-// One persistent CTA per SM walks work items (weight tile, activation tile, K split).  Warp roles:
-//   warp 0            TMA producer: per 64-wide K block one [MT x 64] fp16 activation box and one
+// One persistent CTA per SM walks work items (weight tile, activation tile(s), K split).  Roles:
+//   warp 0            TMA producer: per 64-wide K block the [MT x 64] fp16 activation box(es) and one
 //                     [128 x 32 B] packed-weight box (32-byte swizzle) into a shared-memory stage
 //   warp 1            MMA issuer: four tcgen05.mma kind::f16 (A from TMEM, B from smem, K = 16 each)
-//   warps 2..         convert warps (DQ groups of 4): thread = weight row; 2 x LDS.128 of packed
-//                     nibbles -> 64 fp16 -> tcgen05.st into one of AST operand stages in TMEM
-//   last 4 warps      epilogue: tcgen05.ld the finished accumulator (two buffers), cast, store
+//                     per activation tile and K block, then ONE tcgen05.commit that both frees the
+//                     smem stage and tells the convert warps the TMEM operand stage was consumed
+//   warps 2..9        convert warps (two groups of 4 taking alternate K blocks): thread = weight row;
+//                     2 x LDS.128 of packed nibbles -> 64 fp16 -> tcgen05.st into an operand stage
+//   warps 10..13      epilogue: tcgen05.ld the finished accumulator, cast, store
 // With a K split > 1 the epilogue writes fp32 partials to the caller's workspace and a second
 // kernel sums them in a fixed order (deterministic).  Every wait is bounded (see common.cuh).
 #include "common.cuh"
@@ -28,13 +32,17 @@ constexpr int kBK = 64;        // K per stage: 64 fp16 = one 128-byte swizzle ro
 constexpr int kWBytes = kBNW * (kBK / 2);   // 4096 packed bytes per stage
 constexpr int kGroupN = 16;    // tile-order grouping for L2 reuse
 
-template <int MT> struct W4Cfg {
-    static constexpr int kDQ = MT <= 32 ? 2 : 1;                 // convert warp groups
-    static constexpr int kActBytes = MT * kBK * 2;
-    static constexpr int kStageBytes = kActBytes + kWBytes;
-    static constexpr int kStages = MT <= 32 ? 16 : (MT == 64 ? 12 : 8);
-    static constexpr int kAStages = MT <= 32 ? 8 : 4;            // TMEM operand stages, 32 columns each
-    static constexpr int kDCols = 2 * MT;                        // two accumulator buffers
+// MT = activation rows per MMA (MMA N); PAIR = activation tiles per work item (1 or 2).
+template <int MT, int PAIR> struct W4Cfg {
+    static constexpr int kDQ = 2;                                // convert warp groups (alternate K blocks)
+    static constexpr int kActBytes = MT * kBK * 2;               // one activation tile
+    static constexpr int kStageBytes = PAIR * kActBytes + kWBytes;
+    static constexpr int kStages = MT <= 32 ? 16 : (MT == 64 ? 12 : (PAIR == 2 ? 6 : 8));
+    // TMEM operand stages, 32 columns each; never deeper than the smem ring, because a convert warp
+    // learns that an operand stage was consumed from the smem stage barrier of that same K block
+    static constexpr int kAStages = kStages < 8 ? kStages : 8;
+    static_assert(kAStages <= kStages && kAStages % kDQ == 0, "operand ring must fit the smem ring");
+    static constexpr int kDCols = 2 * MT;                        // two accumulators (alternating, or the pair)
     static constexpr int kACol0 = kDCols;
     static constexpr int kTmemNeed = kDCols + 32 * kAStages;
     static constexpr int kTmemCols = kTmemNeed <= 32 ? 32 : kTmemNeed <= 64 ? 64 : kTmemNeed <= 128 ? 128
@@ -47,6 +55,7 @@ template <int MT> struct W4Cfg {
 };
 
 struct Item { int n_blk, m_blk, kb0, kb1, ks; };
+// tiles_m counts activation units of MT * PAIR rows.
 __device__ __forceinline__ Item make_item(int w, int tiles_n, int tiles_m, int splitk, int KB) {
     const int tile = w / splitk;
     const int ks = w - tile * splitk;
@@ -78,45 +87,45 @@ __device__ __forceinline__ uint32_t dq_pair(uint32_t lo, uint32_t hi, uint32_t s
 
 using namespace tb200;
 
-template <int MT>
+template <int MT, int PAIR>
 __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ tmap_act, const CUtensorMap* __restrict__ tmap_w,
                                                 const __half* __restrict__ scales, __half* __restrict__ out,
                                                 float* __restrict__ ws, int M, int N, int K, int groups_per_row,
                                                 int kb_per_group, int64_t ldo, int64_t col_offset, int splitk,
                                                 float zp_plus_1024) {
-    using Cfg = W4Cfg<MT>;
+    using Cfg = W4Cfg<MT, PAIR>;
     constexpr int S = Cfg::kStages;
     constexpr int AST = Cfg::kAStages;
     constexpr int DQ = Cfg::kDQ;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);   // TMA landed
-    uint64_t* bar_empty = bar_full + S;                                              // MMA done with the stage
-    uint64_t* bar_afull = bar_empty + S;                                             // operand stage written
-    uint64_t* bar_aempty = bar_afull + AST;                                          // operand stage consumed
-    uint64_t* bar_dfull = bar_aempty + AST;                                          // accumulator complete
-    uint64_t* bar_dempty = bar_dfull + 2;                                            // accumulator drained
+    uint64_t* bar_empty = bar_full + S;       // MMAs of the K block complete: smem stage and operand stage free
+    uint64_t* bar_afull = bar_empty + S;      // operand stage written
+    uint64_t* bar_dfull = bar_afull + AST;    // accumulator complete
+    uint64_t* bar_dempty = bar_dfull + 2;     // accumulator drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_dempty + 2);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int KB = K / kBK;
     const int tiles_n = N / kBNW;
-    const int tiles_m = (M + MT - 1) / MT;
+    const int tiles_m = (M + MT * PAIR - 1) / (MT * PAIR);
     const int items = tiles_n * tiles_m * splitk;
+    // Accumulator bookkeeping.  PAIR == 1: the two accumulators alternate between items.
+    // PAIR == 2: accumulator t belongs to activation tile t of every item.
+    auto acc_of = [](uint32_t item_cnt, int t) { return PAIR == 2 ? t : static_cast<int>(item_cnt & 1); };
+    auto acc_use = [](uint32_t item_cnt) { return PAIR == 2 ? item_cnt : (item_cnt >> 1); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(&bar_full[s], 1);
             mbar_init(&bar_empty[s], 1);
         }
-        for (int s = 0; s < AST; ++s) {
-            mbar_init(&bar_afull[s], 128);
-            mbar_init(&bar_aempty[s], 1);
-        }
+        for (int s = 0; s < AST; ++s) mbar_init(&bar_afull[s], 4);   // one arrival per convert warp of the owning group
         for (int b = 0; b < 2; ++b) {
             mbar_init(&bar_dfull[b], 1);
-            mbar_init(&bar_dempty[b], 128);
+            mbar_init(&bar_dempty[b], 4);                            // one arrival per epilogue warp
         }
         mbar_fence_init();
         tma_prefetch_desc(tmap_act);
@@ -138,16 +147,20 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
             bool ok = true;
             for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
                 const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
+                const int m0 = im.m_blk * MT * PAIR;
+                const bool second = PAIR == 2 && m0 + MT < M;
                 for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
                     const int s = it % S;
                     if (!mbar_wait(&bar_empty[s], ((it / S) & 1) ^ 1, ST_WAIT_SMEM_EMPTY, kb)) { ok = false; break; }
                     uint8_t* stage = smem + s * Cfg::kStageBytes;
-                    mbar_expect_tx(&bar_full[s], Cfg::kStageBytes);
-                    tma_load_2d(stage, tmap_act, &bar_full[s], kb * kBK, im.m_blk * MT);
-                    tma_load_2d(stage + Cfg::kActBytes, tmap_w, &bar_full[s], kb * (kBK / 2), im.n_blk * kBNW);
+                    mbar_expect_tx(&bar_full[s], kWBytes + (second ? 2 : 1) * Cfg::kActBytes);
+                    tma_load_2d(stage, tmap_act, &bar_full[s], kb * kBK, m0);
+                    if (second) tma_load_2d(stage + Cfg::kActBytes, tmap_act, &bar_full[s], kb * kBK, m0 + MT);
+                    tma_load_2d(stage + PAIR * Cfg::kActBytes, tmap_w, &bar_full[s], kb * (kBK / 2), im.n_blk * kBNW);
                 }
             }
             if (!ok) {
+                // give copies already in flight a bounded chance to land before the CTA exits
                 for (int s = 0; s < S; ++s) {
                     if (it > static_cast<uint32_t>(s)) {
                         uint32_t last = it - 1 - ((it - 1 - s) % S);
@@ -164,26 +177,35 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
             bool ok = true;
             for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++item_cnt) {
                 const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
-                const int dbuf = item_cnt & 1;
-                if (!mbar_wait(&bar_dempty[dbuf], ((item_cnt >> 1) & 1) ^ 1, ST_WAIT_TMEM_EMPTY, w)) { ok = false; break; }
-                const uint32_t d_tmem = tmem_base + dbuf * MT;
-                for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
+                const bool second = PAIR == 2 && im.m_blk * MT * PAIR + MT < M;
+                const uint32_t use = acc_use(item_cnt);
+                for (int kb = im.kb0; kb < im.kb1 && ok; ++kb, ++it) {
                     const int s = it % S;
                     const int as = it % AST;
                     if (!mbar_wait(&bar_full[s], (it / S) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
                     if (!mbar_wait(&bar_afull[as], (it / AST) & 1, ST_WAIT_OPERAND, kb)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint64_t b_desc = umma_desc_sw128(smem_u32(smem + s * Cfg::kStageBytes));
                     const uint32_t a_tmem = tmem_base + Cfg::kACol0 + as * 32;
 #pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k) {
-                        // 16 fp16 of K = 8 TMEM columns of the operand, 32 bytes of the swizzled smem row
-                        umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, (kb > im.kb0 || k > 0) ? 1u : 0u);
+                    for (int t = 0; t < PAIR; ++t) {
+                        const int acc = acc_of(item_cnt, t);
+                        if (kb == im.kb0) {   // first write of this accumulator in the item: it must be drained
+                            if (!mbar_wait(&bar_dempty[acc], (use & 1) ^ 1, ST_WAIT_TMEM_EMPTY, w)) { ok = false; break; }
+                        }
+                        if (t == 1 && !second) break;
+                        tc_fence_after();
+                        const uint64_t b_desc = umma_desc_sw128(smem_u32(smem + s * Cfg::kStageBytes + t * Cfg::kActBytes));
+                        const uint32_t d_tmem = tmem_base + acc * MT;
+#pragma unroll
+                        for (int k = 0; k < kBK / 16; ++k) {
+                            // 16 fp16 of K = 8 TMEM columns of the operand, 32 bytes of the swizzled smem row
+                            umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, (kb > im.kb0 || k > 0) ? 1u : 0u);
+                        }
                     }
+                    // one commit per K block frees both the smem stage (producer) and the TMEM
+                    // operand stage (convert warps, which wait on the same barrier)
                     tc_commit(&bar_empty[s]);
-                    tc_commit(&bar_aempty[as]);
                 }
-                if (ok) tc_commit(&bar_dfull[dbuf]);
+                if (ok) tc_commit(&bar_dfull[PAIR == 2 ? 0 : acc_of(item_cnt, 0)]);
             }
         }
     } else if (warp < Cfg::kEpiWarp0) {
@@ -196,38 +218,77 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         // physical offset of this row's two 16-byte chunks under the 32-byte TMA swizzle
         const uint32_t swz = ((row >> 2) & 1) << 4;
         const uint32_t off0 = row * 32 + (0u ^ swz), off1 = row * 32 + (16u ^ swz);
+        const int g_last = groups_per_row - 1;
+        auto scale_at = [&](const __half* srow, int g) { return __ldg(srow + min(g, g_last)); };
+        auto scale_row = [&](const Item& im) {
+            return scales + static_cast<int64_t>(im.n_blk * kBNW + row) * groups_per_row;
+        };
+        // Scales are fetched three groups ahead of their use (s0 = current group), and the first
+        // three of the next work item while the current one runs, so no load sits on the K loop.
+        __half s0, s1, s2, n0 = __half(), n1 = __half(), n2 = __half();
+        if (static_cast<int>(blockIdx.x) < items) {
+            const Item im = make_item(blockIdx.x, tiles_n, tiles_m, splitk, KB);
+            const __half* srow = scale_row(im);
+            const int g = im.kb0 / kb_per_group;
+            n0 = scale_at(srow, g); n1 = scale_at(srow, g + 1); n2 = scale_at(srow, g + 2);
+        }
         uint32_t it = 0;
         bool ok = true;
+        int pending_as = -1;                             // operand stage stored but not yet published
         for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
             const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
-            const __half* srow = scales + static_cast<int64_t>(im.n_blk * kBNW + row) * groups_per_row;
+            const __half* srow = scale_row(im);
+            int gcur = im.kb0 / kb_per_group;
+            s0 = n0; s1 = n1; s2 = n2;
+            if (w + static_cast<int>(gridDim.x) < items) {
+                const Item nx = make_item(w + gridDim.x, tiles_n, tiles_m, splitk, KB);
+                const __half* nrow = scale_row(nx);
+                const int g = nx.kb0 / kb_per_group;
+                n0 = scale_at(nrow, g); n1 = scale_at(nrow, g + 1); n2 = scale_at(nrow, g + 2);
+            }
             for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
                 if (static_cast<int>(it % DQ) != grp) continue;
                 const int s = it % S;
                 const int as = it % AST;
-                const __half sc = __ldg(srow + kb / kb_per_group);
+                const int g = kb / kb_per_group;
+                while (gcur < g) { s0 = s1; s1 = s2; s2 = scale_at(srow, gcur + 3); ++gcur; }
                 if (!mbar_wait(&bar_full[s], (it / S) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
-                const uint8_t* wt = smem + s * Cfg::kStageBytes + Cfg::kActBytes;
+                const uint8_t* wt = smem + s * Cfg::kStageBytes + PAIR * Cfg::kActBytes;
                 const uint4 p0 = *reinterpret_cast<const uint4*>(wt + off0);
                 const uint4 p1 = *reinterpret_cast<const uint4*>(wt + off1);
-                const __half2 s2 = __half2half2(sc);
+                const __half2 s2h = __half2half2(s0);
                 uint32_t frag[32];
                 const uint32_t pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const uint32_t lo = pw[i], hi = pw[i] >> 4;
-                    frag[4 * i + 0] = dq_pair(lo, hi, 0x0400, bias, s2);
-                    frag[4 * i + 1] = dq_pair(lo, hi, 0x0501, bias, s2);
-                    frag[4 * i + 2] = dq_pair(lo, hi, 0x0602, bias, s2);
-                    frag[4 * i + 3] = dq_pair(lo, hi, 0x0703, bias, s2);
+                    frag[4 * i + 0] = dq_pair(lo, hi, 0x0400, bias, s2h);
+                    frag[4 * i + 1] = dq_pair(lo, hi, 0x0501, bias, s2h);
+                    frag[4 * i + 2] = dq_pair(lo, hi, 0x0602, bias, s2h);
+                    frag[4 * i + 3] = dq_pair(lo, hi, 0x0703, bias, s2h);
                 }
-                if (!mbar_wait(&bar_aempty[as], ((it / AST) & 1) ^ 1, ST_WAIT_OPERAND, -kb - 1)) { ok = false; break; }
+                // publish the previous block's stage: its tcgen05.st had this block's unpack to complete
+                if (pending_as >= 0) {
+                    tmem_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar_afull[pending_as]);
+                    pending_as = -1;
+                }
+                if (it >= static_cast<uint32_t>(AST)) {      // the MMAs that last read this operand stage
+                    const uint32_t j = it - AST;
+                    if (!mbar_wait(&bar_empty[j % S], (j / S) & 1, ST_WAIT_OPERAND, -kb - 1)) { ok = false; break; }
+                }
                 tc_fence_after();
                 tmem_st32(t_lane + as * 32, frag);
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(&bar_afull[as]);
+                pending_as = as;
             }
+        }
+        if (pending_as >= 0) {
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_afull[pending_as]);
         }
     } else {
         // ---------------- epilogue warps ----------------
@@ -238,32 +299,40 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         bool ok = true;
         for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++item_cnt) {
             const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
-            const int dbuf = item_cnt & 1;
-            if (!mbar_wait(&bar_dfull[dbuf], (item_cnt >> 1) & 1, ST_WAIT_TMEM_FULL, w)) { ok = false; break; }
+            const uint32_t use = acc_use(item_cnt);
+            if (!mbar_wait(&bar_dfull[PAIR == 2 ? 0 : acc_of(item_cnt, 0)], use & 1, ST_WAIT_TMEM_FULL, w)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + dbuf * MT;
             const int64_t n = static_cast<int64_t>(im.n_blk) * kBNW + row;
 #pragma unroll
-            for (int c = 0; c < MT / kChunk; ++c) {
-                uint32_t v[kChunk];
-                if constexpr (kChunk == 32) tmem_ld32(t_lane + c * kChunk, v);
-                else                        tmem_ld16(t_lane + c * kChunk, v);
-                tmem_wait_ld();
-                const int m0 = im.m_blk * MT + c * kChunk;
-                if (splitk == 1) {
-                    __half* dst = out + col_offset + n;
+            for (int t = 0; t < PAIR; ++t) {
+                const int acc = acc_of(item_cnt, t);
+                const int mt0 = im.m_blk * MT * PAIR + t * MT;
+                const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + acc * MT;
+                if (mt0 < M) {
 #pragma unroll
-                    for (int j = 0; j < kChunk; ++j)
-                        if (m0 + j < M) dst[static_cast<int64_t>(m0 + j) * ldo] = __float2half_rn(__uint_as_float(v[j]));
-                } else {
-                    float* dst = ws + static_cast<int64_t>(im.ks) * M * N + n;
+                    for (int c = 0; c < MT / kChunk; ++c) {
+                        uint32_t v[kChunk];
+                        if constexpr (kChunk == 32) tmem_ld32(t_lane + c * kChunk, v);
+                        else                        tmem_ld16(t_lane + c * kChunk, v);
+                        tmem_wait_ld();
+                        const int m0 = mt0 + c * kChunk;
+                        if (splitk == 1) {
+                            __half* dst = out + col_offset + n;
 #pragma unroll
-                    for (int j = 0; j < kChunk; ++j)
-                        if (m0 + j < M) dst[static_cast<int64_t>(m0 + j) * N] = __uint_as_float(v[j]);
+                            for (int j = 0; j < kChunk; ++j)
+                                if (m0 + j < M) dst[static_cast<int64_t>(m0 + j) * ldo] = __float2half_rn(__uint_as_float(v[j]));
+                        } else {
+                            float* dst = ws + static_cast<int64_t>(im.ks) * M * N + n;
+#pragma unroll
+                            for (int j = 0; j < kChunk; ++j)
+                                if (m0 + j < M) dst[static_cast<int64_t>(m0 + j) * N] = __uint_as_float(v[j]);
+                        }
+                    }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_dempty[acc]);
             }
-            tc_fence_before();
-            mbar_arrive(&bar_dempty[dbuf]);
         }
     }
 
@@ -276,17 +345,18 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
     }
 }
 
-#define TB200_W4_KERNEL(MT)                                                                                        \
-    extern "C" __global__ void __launch_bounds__(W4Cfg<MT>::kThreads, 1) tb200_k_gemm_w4a16_m##MT(                 \
+#define TB200_W4_KERNEL(NAME, MT, PAIR)                                                                            \
+    extern "C" __global__ void __launch_bounds__(W4Cfg<MT, PAIR>::kThreads, 1) tb200_k_gemm_w4a16_##NAME(          \
         const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_w,                  \
         const __half* scales, __half* out, float* ws, int M, int N, int K, int gpr, int kbpg, int64_t ldo,         \
         int64_t col_offset, int splitk, float zp1024) {                                                            \
-        gemm_w4a16_body<MT>(&tmap_act, &tmap_w, scales, out, ws, M, N, K, gpr, kbpg, ldo, col_offset, splitk,      \
-                            zp1024);                                                                               \
+        gemm_w4a16_body<MT, PAIR>(&tmap_act, &tmap_w, scales, out, ws, M, N, K, gpr, kbpg, ldo, col_offset,        \
+                                  splitk, zp1024);                                                                 \
     }
-TB200_W4_KERNEL(16)
-TB200_W4_KERNEL(64)
-TB200_W4_KERNEL(128)
+TB200_W4_KERNEL(m16, 16, 1)
+TB200_W4_KERNEL(m64, 64, 1)
+TB200_W4_KERNEL(m128, 128, 1)
+TB200_W4_KERNEL(m256, 128, 2)
 
 // out[m, col_offset + n] = fp16( ws[0][m][n] + ws[1][m][n] + ... ) — fixed order, 4 columns per thread.
 extern "C" __global__ void __launch_bounds__(256)
@@ -341,10 +411,10 @@ int pick_splitk(int64_t m, int64_t n, int64_t k) {
     return best;
 }
 
-template <int MT, typename Kern>
+template <int MT, int PAIR, typename Kern>
 int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void* out, float* ws, int64_t m, int64_t n,
               int64_t k, int64_t group, int zp, int64_t ldo, int64_t col_offset, int splitk, cudaStream_t st) {
-    using Cfg = W4Cfg<MT>;
+    using Cfg = W4Cfg<MT, PAIR>;
     static bool attr_set[64] = {false};
     int dev = 0;
     TB200_CUDA_TRY(cudaGetDevice(&dev));
@@ -357,7 +427,7 @@ int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void
     if (rc != TB200_OK) return rc;
     rc = encode_tmap_2d(&tw, wp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k / 2, k / 2, kBNW, kBK / 2, CU_TENSOR_MAP_SWIZZLE_32B);
     if (rc != TB200_OK) return rc;
-    const int64_t items = (n / kBNW) * ((m + MT - 1) / MT) * splitk;
+    const int64_t items = (n / kBNW) * ((m + MT * PAIR - 1) / (MT * PAIR)) * splitk;
     const int grid = static_cast<int>(items < num_sms() ? items : num_sms());
     kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(ta, tw, static_cast<const __half*>(scales), static_cast<__half*>(out), ws,
                                                         static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
@@ -408,9 +478,11 @@ extern "C" int tb200_gemm_w4a16(const void* a, const void* wp, const void* scale
         ws = static_cast<float*>(workspace);
     }
     switch (pick_mt(m)) {
-        case 16:  return launch_w4<16>(tb200_k_gemm_w4a16_m16, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
-        case 64:  return launch_w4<64>(tb200_k_gemm_w4a16_m64, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
-        default:  return launch_w4<128>(tb200_k_gemm_w4a16_m128, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
+        case 16:  return launch_w4<16, 1>(tb200_k_gemm_w4a16_m16, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
+        case 64:  return launch_w4<64, 1>(tb200_k_gemm_w4a16_m64, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
+        default:
+            if (m > 128) return launch_w4<128, 2>(tb200_k_gemm_w4a16_m256, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
+            return launch_w4<128, 1>(tb200_k_gemm_w4a16_m128, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
     }
 }
 
