@@ -142,10 +142,12 @@ def test_w4a16_config_shape_m4096_vs_torch_reference(cuda_device):
     assert torch.equal(out, impl_cuda.run(*inputs))     # deterministic, split-K or not
 
 
-def test_w4a16_column_offset_writes_only_its_slice(cuda_device):
-    """N-partition building block: two calls with col_offset fill one [M, N] buffer; guard columns stay."""
+@pytest.mark.parametrize("M", [64, 300])
+def test_w4a16_column_offset_writes_only_its_slice(cuda_device, M):
+    """N-partition building block: two calls with col_offset fill one [M, N] buffer; guard columns stay.
+    M = 300 takes the 256-row tiles whose epilogue goes through shared memory and TMA stores (clipped at M)."""
     ext = native.load()
-    M, N, K = 64, 512, 512
+    N, K = 512, 512
     a, wp, sc, group, zp = tensors.generate_gemm_w4a16_inputs(M, K, N, device="cpu", seed=8)
     ad, wpd, scd = a.to(cuda_device), wp.to(cuda_device), sc.to(cuda_device)
     out = torch.full((M, N + 64), 7.0, dtype=torch.float16, device=cuda_device)

@@ -5,19 +5,28 @@
 // the tensor-memory operand of tcgen05.mma: the convert warps unpack int4 to fp16 in registers and
 // write the fragments straight into TMEM with tcgen05.st — the dequantised tile never goes back
 // through shared memory.  Activations arrive by TMA as the 128-byte-swizzled shared-memory operand
-// with MMA-N = the activation-row tile MT (16 for decode-sized m, 64, or 128).  For m > 128 one
-// work item covers TWO 128-row activation tiles that share every converted weight stage (two
-// accumulators), which halves the convert and hand-off work per flop.
+// with MMA-N = the activation-row tile MT (16 for decode-sized m, 64, 128, or 256 for m > 128:
+// issuing a tcgen05.mma costs the issuing thread roughly 90 cycles whatever its size, so only
+// N = 256 instructions (128 cycles of tensor work each) keep the tensor pipe ahead of the issuer).
 //
-// One persistent CTA per SM walks work items (weight tile, activation tile(s), K split).  Roles:
-//   warp 0            TMA producer: per 64-wide K block the [MT x 64] fp16 activation box(es) and one
-//                     [128 x 32 B] packed-weight box (32-byte swizzle) into a shared-memory stage
-//   warp 1            MMA issuer: four tcgen05.mma kind::f16 (A from TMEM, B from smem, K = 16 each)
-//                     per activation tile and K block, then ONE tcgen05.commit that both frees the
-//                     smem stage and tells the convert warps the TMEM operand stage was consumed
-//   warps 2..9        convert warps (two groups of 4 taking alternate K blocks): thread = weight row;
+// One persistent CTA per SM walks work items (weight tile, activation tile(s), K split).  Three
+// rings decouple the roles, so the small packed-weight stream runs far ahead of the wide
+// activation stream and the TMA + unpack latency stays off the MMA's critical path:
+//   packed weights  smem, SW stages of [128 x 32 B] (32-byte swizzle)   TMA (warp 1)  -> convert warps
+//   fp16 operand    TMEM, AST stages of 32 columns                      convert warps -> MMA
+//   activations     smem, SA stages of [MT x 64] fp16 (128-byte swizzle)         TMA (warp 0) -> MMA
+// Roles:
+//   warp 0            activation TMA producer
+//   warp 1            packed-weight TMA producer
+//   warp 2            MMA issuer: four tcgen05.mma kind::f16 (A from TMEM, B from smem, K = 16 each) per
+//                     64-wide K block, then ONE tcgen05.commit: "MMAs of this K block complete" frees
+//                     the activation stage and the operand stage (same ring depth, same barrier)
+//   warp 3            idle (keeps the following warp quads aligned with the TMEM lane quarters)
+//   warps 4..11       convert warps (two groups of 4 taking alternate K blocks): thread = weight row;
 //                     2 x LDS.128 of packed nibbles -> 64 fp16 -> tcgen05.st into an operand stage
-//   warps 10..13      epilogue: tcgen05.ld the finished accumulator, cast, store
+//   warps 12..15      epilogue: tcgen05.ld the finished accumulator, cast; for MT >= 128 transpose
+//                     through a shared-memory tile and write it with one TMA store per 128 rows,
+//                     otherwise store directly (fp32 split-K partials or fp16)
 // With a K split > 1 the epilogue writes fp32 partials to the caller's workspace and a second
 // kernel sums them in a fixed order (deterministic).  Every wait is bounded (see common.cuh).
 #include "common.cuh"
@@ -29,33 +38,42 @@ namespace {
 
 constexpr int kBNW = 128;      // weight rows per tile (MMA M)
 constexpr int kBK = 64;        // K per stage: 64 fp16 = one 128-byte swizzle row
-constexpr int kWBytes = kBNW * (kBK / 2);   // 4096 packed bytes per stage
+constexpr int kWBytes = kBNW * (kBK / 2);   // 4096 packed bytes per weight stage
 constexpr int kGroupN = 16;    // tile-order grouping for L2 reuse
 
-// MT = activation rows per MMA (MMA N); PAIR = activation tiles per work item (1 or 2).
-template <int MT, int PAIR> struct W4Cfg {
+// MT = activation rows per work item = MMA N.
+template <int MT> struct W4Cfg {
     static constexpr int kDQ = 2;                                // convert warp groups (alternate K blocks)
-    static constexpr int kActBytes = MT * kBK * 2;               // one activation tile
-    static constexpr int kStageBytes = PAIR * kActBytes + kWBytes;
-    static constexpr int kStages = MT <= 32 ? 16 : (MT == 64 ? 12 : (PAIR == 2 ? 6 : 8));
-    // TMEM operand stages, 32 columns each; never deeper than the smem ring, because a convert warp
-    // learns that an operand stage was consumed from the smem stage barrier of that same K block
-    static constexpr int kAStages = kStages < 8 ? kStages : 8;
-    static_assert(kAStages <= kStages && kAStages % kDQ == 0, "operand ring must fit the smem ring");
-    static constexpr int kDCols = 2 * MT;                        // two accumulators (alternating, or the pair)
+    static constexpr int kActStageBytes = MT * kBK * 2;          // one [MT x 64] fp16 activation tile
+    static constexpr int kNAcc = MT == 256 ? 1 : 2;              // accumulators (256 columns fill TMEM once)
+    static constexpr bool kTmaStore = MT >= 128;                 // epilogue through smem + TMA store
+    static constexpr int kStoreBytes = kTmaStore ? 128 * kBNW * 2 : 0;   // [128 m x 128 n] fp16 staging tile
+    static constexpr int kSA = MT <= 32 ? 16 : (MT == 64 ? 12 : (MT == 128 ? 8 : 5));   // activation stages
+    static constexpr int kSW = MT <= 32 ? 32 : (MT == 256 ? 8 : 16);                    // packed-weight stages
+    // TMEM operand stages, 32 columns each: as deep as the activation ring, because both are freed by
+    // the same per-K-block commit and share its barrier
+    static constexpr int kAStages = kSA < 8 ? kSA : 8;
+    static constexpr int kDCols = kNAcc * MT;
     static constexpr int kACol0 = kDCols;
     static constexpr int kTmemNeed = kDCols + 32 * kAStages;
     static constexpr int kTmemCols = kTmemNeed <= 32 ? 32 : kTmemNeed <= 64 ? 64 : kTmemNeed <= 128 ? 128
                                      : kTmemNeed <= 256 ? 256 : 512;
-    static constexpr int kWarps = 2 + 4 * kDQ + 4;
+    static constexpr int kCvtWarp0 = 4;
+    static constexpr int kEpiWarp0 = kCvtWarp0 + 4 * kDQ;
+    static constexpr int kWarps = kEpiWarp0 + 4;
     static constexpr int kThreads = 32 * kWarps;
-    static constexpr int kEpiWarp0 = 2 + 4 * kDQ;
-    static constexpr int kBarBytes = 512;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;
+    static constexpr int kActRingBytes = kSA * kActStageBytes;
+    static constexpr int kWRingBytes = kSW * kWBytes;
+    static constexpr int kBarBytes = 1024;
+    static constexpr int kSmemBytes = kActRingBytes + kWRingBytes + kStoreBytes + kBarBytes + 1024;
+    static_assert(kAStages <= kSA, "operand ring must not be deeper than the activation ring");
+    static_assert(kTmemNeed <= 512, "TMEM over-subscribed");
+    static_assert((2 * kSA + 2 * kSW + kAStages + 4) * 8 + 8 <= kBarBytes, "barrier block too small");
+    static_assert(kSmemBytes <= 232448, "over the 227 KB shared-memory limit");
 };
 
 struct Item { int n_blk, m_blk, kb0, kb1, ks; };
-// tiles_m counts activation units of MT * PAIR rows.
+// tiles_m counts activation tiles of MT rows.
 __device__ __forceinline__ Item make_item(int w, int tiles_n, int tiles_m, int splitk, int KB) {
     const int tile = w / splitk;
     const int ks = w - tile * splitk;
@@ -87,22 +105,30 @@ __device__ __forceinline__ uint32_t dq_pair(uint32_t lo, uint32_t hi, uint32_t s
 
 using namespace tb200;
 
-template <int MT, int PAIR>
+template <int MT>
 __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ tmap_act, const CUtensorMap* __restrict__ tmap_w,
+                                                const CUtensorMap* __restrict__ tmap_out,
                                                 const __half* __restrict__ scales, __half* __restrict__ out,
                                                 float* __restrict__ ws, int M, int N, int K, int groups_per_row,
                                                 int kb_per_group, int64_t ldo, int64_t col_offset, int splitk,
-                                                float zp_plus_1024) {
-    using Cfg = W4Cfg<MT, PAIR>;
-    constexpr int S = Cfg::kStages;
+                                                float zp_plus_1024, int tma_store) {
+    using Cfg = W4Cfg<MT>;
+    constexpr int SA = Cfg::kSA;
+    constexpr int SW = Cfg::kSW;
     constexpr int AST = Cfg::kAStages;
     constexpr int DQ = Cfg::kDQ;
+    constexpr int NACC = Cfg::kNAcc;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);   // TMA landed
-    uint64_t* bar_empty = bar_full + S;       // MMAs of the K block complete: smem stage and operand stage free
-    uint64_t* bar_afull = bar_empty + S;      // operand stage written
-    uint64_t* bar_dfull = bar_afull + AST;    // accumulator complete
+    uint8_t* act_ring = smem;
+    uint8_t* w_ring = smem + Cfg::kActRingBytes;
+    uint8_t* store_tile = w_ring + Cfg::kWRingBytes;
+    uint64_t* bar_afull = reinterpret_cast<uint64_t*>(store_tile + Cfg::kStoreBytes);
+    uint64_t* bar_done = bar_afull + SA;      // MMAs of a K block complete: activation stage and operand stage free
+    uint64_t* bar_wfull = bar_done + SA;      // packed-weight stage: TMA landed
+    uint64_t* bar_wempty = bar_wfull + SW;    //                      convert warps have read it
+    uint64_t* bar_ofull = bar_wempty + SW;    // TMEM operand stage written by the convert warps
+    uint64_t* bar_dfull = bar_ofull + AST;    // accumulator complete
     uint64_t* bar_dempty = bar_dfull + 2;     // accumulator drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_dempty + 2);
 
@@ -110,28 +136,23 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
     const int lane = threadIdx.x & 31;
     const int KB = K / kBK;
     const int tiles_n = N / kBNW;
-    const int tiles_m = (M + MT * PAIR - 1) / (MT * PAIR);
+    const int tiles_m = (M + MT - 1) / MT;
     const int items = tiles_n * tiles_m * splitk;
-    // Accumulator bookkeeping.  PAIR == 1: the two accumulators alternate between items.
-    // PAIR == 2: accumulator t belongs to activation tile t of every item.
-    auto acc_of = [](uint32_t item_cnt, int t) { return PAIR == 2 ? t : static_cast<int>(item_cnt & 1); };
-    auto acc_use = [](uint32_t item_cnt) { return PAIR == 2 ? item_cnt : (item_cnt >> 1); };
+    // accumulator of an item and how often it was used before (phase of its barriers)
+    auto acc_of = [](uint32_t item_cnt) { return NACC == 1 ? 0 : static_cast<int>(item_cnt & 1); };
+    auto acc_use = [](uint32_t item_cnt) { return NACC == 1 ? item_cnt : (item_cnt >> 1); };
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < S; ++s) {
-            mbar_init(&bar_full[s], 1);
-            mbar_init(&bar_empty[s], 1);
-        }
-        for (int s = 0; s < AST; ++s) mbar_init(&bar_afull[s], 4);   // one arrival per convert warp of the owning group
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&bar_dfull[b], 1);
-            mbar_init(&bar_dempty[b], 4);                            // one arrival per epilogue warp
-        }
+        for (int s = 0; s < SA; ++s) { mbar_init(&bar_afull[s], 1); mbar_init(&bar_done[s], 1); }
+        for (int s = 0; s < SW; ++s) { mbar_init(&bar_wfull[s], 1); mbar_init(&bar_wempty[s], 4); }
+        for (int s = 0; s < AST; ++s) mbar_init(&bar_ofull[s], 4);
+        for (int b = 0; b < 2; ++b) { mbar_init(&bar_dfull[b], 1); mbar_init(&bar_dempty[b], 4); }
         mbar_fence_init();
         tma_prefetch_desc(tmap_act);
         tma_prefetch_desc(tmap_w);
+        if (Cfg::kTmaStore && tma_store) tma_prefetch_desc(tmap_out);
     }
-    if (warp == 1) {
+    if (warp == 2) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
         tmem_relinquish();
     }
@@ -141,35 +162,52 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- activation TMA producer ----------------
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
                 const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
-                const int m0 = im.m_blk * MT * PAIR;
-                const bool second = PAIR == 2 && m0 + MT < M;
                 for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
-                    const int s = it % S;
-                    if (!mbar_wait(&bar_empty[s], ((it / S) & 1) ^ 1, ST_WAIT_SMEM_EMPTY, kb)) { ok = false; break; }
-                    uint8_t* stage = smem + s * Cfg::kStageBytes;
-                    mbar_expect_tx(&bar_full[s], kWBytes + (second ? 2 : 1) * Cfg::kActBytes);
-                    tma_load_2d(stage, tmap_act, &bar_full[s], kb * kBK, m0);
-                    if (second) tma_load_2d(stage + Cfg::kActBytes, tmap_act, &bar_full[s], kb * kBK, m0 + MT);
-                    tma_load_2d(stage + PAIR * Cfg::kActBytes, tmap_w, &bar_full[s], kb * (kBK / 2), im.n_blk * kBNW);
+                    const int s = it % SA;
+                    if (!mbar_wait(&bar_done[s], ((it / SA) & 1) ^ 1, ST_WAIT_SMEM_EMPTY, kb)) { ok = false; break; }
+                    mbar_expect_tx(&bar_afull[s], Cfg::kActStageBytes);
+                    tma_load_2d(act_ring + s * Cfg::kActStageBytes, tmap_act, &bar_afull[s], kb * kBK, im.m_blk * MT);
                 }
             }
-            if (!ok) {
-                // give copies already in flight a bounded chance to land before the CTA exits
-                for (int s = 0; s < S; ++s) {
+            if (!ok) {   // give copies already in flight a bounded chance to land before the CTA exits
+                for (int s = 0; s < SA; ++s) {
                     if (it > static_cast<uint32_t>(s)) {
-                        uint32_t last = it - 1 - ((it - 1 - s) % S);
-                        (void)mbar_wait(&bar_full[s], (last / S) & 1, ST_WAIT_SMEM_FULL, -1);
+                        uint32_t last = it - 1 - ((it - 1 - s) % SA);
+                        (void)mbar_wait(&bar_afull[s], (last / SA) & 1, ST_WAIT_SMEM_FULL, -1);
                     }
                 }
             }
         }
     } else if (warp == 1) {
+        // ---------------- packed-weight TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+                const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
+                for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
+                    const int s = it % SW;
+                    if (!mbar_wait(&bar_wempty[s], ((it / SW) & 1) ^ 1, ST_WAIT_SMEM_EMPTY, -kb - 1)) { ok = false; break; }
+                    mbar_expect_tx(&bar_wfull[s], kWBytes);
+                    tma_load_2d(w_ring + s * kWBytes, tmap_w, &bar_wfull[s], kb * (kBK / 2), im.n_blk * kBNW);
+                }
+            }
+            if (!ok) {
+                for (int s = 0; s < SW; ++s) {
+                    if (it > static_cast<uint32_t>(s)) {
+                        uint32_t last = it - 1 - ((it - 1 - s) % SW);
+                        (void)mbar_wait(&bar_wfull[s], (last / SW) & 1, ST_WAIT_SMEM_FULL, -2);
+                    }
+                }
+            }
+        }
+    } else if (warp == 2) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(0, 0, kBNW, MT);   // f16 x f16 -> f32, M = 128, N = MT
@@ -177,40 +215,31 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
             bool ok = true;
             for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++item_cnt) {
                 const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
-                const bool second = PAIR == 2 && im.m_blk * MT * PAIR + MT < M;
-                const uint32_t use = acc_use(item_cnt);
-                for (int kb = im.kb0; kb < im.kb1 && ok; ++kb, ++it) {
-                    const int s = it % S;
-                    const int as = it % AST;
-                    if (!mbar_wait(&bar_full[s], (it / S) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
-                    if (!mbar_wait(&bar_afull[as], (it / AST) & 1, ST_WAIT_OPERAND, kb)) { ok = false; break; }
-                    const uint32_t a_tmem = tmem_base + Cfg::kACol0 + as * 32;
+                const int acc = acc_of(item_cnt);
+                const uint32_t d_tmem = tmem_base + acc * MT;
+                // the accumulator must have been drained before this item's first MMA overwrites it
+                if (!mbar_wait(&bar_dempty[acc], (acc_use(item_cnt) & 1) ^ 1, ST_WAIT_TMEM_EMPTY, w)) { ok = false; break; }
+                for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
+                    const int s = it % SA;
+                    const int os = it % AST;
+                    if (!mbar_wait(&bar_ofull[os], (it / AST) & 1, ST_WAIT_OPERAND, kb)) { ok = false; break; }
+                    if (!mbar_wait(&bar_afull[s], (it / SA) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_tmem = tmem_base + Cfg::kACol0 + os * 32;
+                    const uint64_t b_desc = umma_desc_sw128(smem_u32(act_ring + s * Cfg::kActStageBytes));
 #pragma unroll
-                    for (int t = 0; t < PAIR; ++t) {
-                        const int acc = acc_of(item_cnt, t);
-                        if (kb == im.kb0) {   // first write of this accumulator in the item: it must be drained
-                            if (!mbar_wait(&bar_dempty[acc], (use & 1) ^ 1, ST_WAIT_TMEM_EMPTY, w)) { ok = false; break; }
-                        }
-                        if (t == 1 && !second) break;
-                        tc_fence_after();
-                        const uint64_t b_desc = umma_desc_sw128(smem_u32(smem + s * Cfg::kStageBytes + t * Cfg::kActBytes));
-                        const uint32_t d_tmem = tmem_base + acc * MT;
-#pragma unroll
-                        for (int k = 0; k < kBK / 16; ++k) {
-                            // 16 fp16 of K = 8 TMEM columns of the operand, 32 bytes of the swizzled smem row
-                            umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, (kb > im.kb0 || k > 0) ? 1u : 0u);
-                        }
+                    for (int k = 0; k < kBK / 16; ++k) {
+                        // 16 fp16 of K = 8 TMEM columns of the operand, 32 bytes of the swizzled smem row
+                        umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, (kb > im.kb0 || k > 0) ? 1u : 0u);
                     }
-                    // one commit per K block frees both the smem stage (producer) and the TMEM
-                    // operand stage (convert warps, which wait on the same barrier)
-                    tc_commit(&bar_empty[s]);
+                    tc_commit(&bar_done[s]);
                 }
-                if (ok) tc_commit(&bar_dfull[PAIR == 2 ? 0 : acc_of(item_cnt, 0)]);
+                if (ok) tc_commit(&bar_dfull[acc]);
             }
         }
-    } else if (warp < Cfg::kEpiWarp0) {
+    } else if (warp >= Cfg::kCvtWarp0 && warp < Cfg::kEpiWarp0) {
         // ---------------- convert warps: packed int4 (smem) -> fp16 operand (TMEM) ----------------
-        const int grp = (warp - 2) >> 2;                 // which K blocks this group takes (it % DQ == grp)
+        const int grp = (warp - Cfg::kCvtWarp0) >> 2;    // which K blocks this group takes (it % DQ == grp)
         const int lane_grp = warp & 3;
         const int row = lane_grp * 32 + lane;            // weight row inside the tile == TMEM lane
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + Cfg::kACol0;
@@ -234,7 +263,6 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         }
         uint32_t it = 0;
         bool ok = true;
-        int pending_as = -1;                             // operand stage stored but not yet published
         for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
             const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
             const __half* srow = scale_row(im);
@@ -248,14 +276,16 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
             }
             for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
                 if (static_cast<int>(it % DQ) != grp) continue;
-                const int s = it % S;
-                const int as = it % AST;
+                const int sw = it % SW;
+                const int os = it % AST;
                 const int g = kb / kb_per_group;
                 while (gcur < g) { s0 = s1; s1 = s2; s2 = scale_at(srow, gcur + 3); ++gcur; }
-                if (!mbar_wait(&bar_full[s], (it / S) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
-                const uint8_t* wt = smem + s * Cfg::kStageBytes + PAIR * Cfg::kActBytes;
+                if (!mbar_wait(&bar_wfull[sw], (it / SW) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
+                const uint8_t* wt = w_ring + sw * kWBytes;
                 const uint4 p0 = *reinterpret_cast<const uint4*>(wt + off0);
                 const uint4 p1 = *reinterpret_cast<const uint4*>(wt + off1);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_wempty[sw]);     // packed bytes are in registers
                 const __half2 s2h = __half2half2(s0);
                 uint32_t frag[32];
                 const uint32_t pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
@@ -267,55 +297,83 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                     frag[4 * i + 2] = dq_pair(lo, hi, 0x0602, bias, s2h);
                     frag[4 * i + 3] = dq_pair(lo, hi, 0x0703, bias, s2h);
                 }
-                // publish the previous block's stage: its tcgen05.st had this block's unpack to complete
-                if (pending_as >= 0) {
-                    tmem_wait_st();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&bar_afull[pending_as]);
-                    pending_as = -1;
-                }
                 if (it >= static_cast<uint32_t>(AST)) {      // the MMAs that last read this operand stage
                     const uint32_t j = it - AST;
-                    if (!mbar_wait(&bar_empty[j % S], (j / S) & 1, ST_WAIT_OPERAND, -kb - 1)) { ok = false; break; }
+                    if (!mbar_wait(&bar_done[j % SA], (j / SA) & 1, ST_WAIT_OPERAND, -kb - 1)) { ok = false; break; }
                 }
                 tc_fence_after();
-                tmem_st32(t_lane + as * 32, frag);
-                pending_as = as;
+                tmem_st32(t_lane + os * 32, frag);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_ofull[os]);
             }
         }
-        if (pending_as >= 0) {
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_afull[pending_as]);
-        }
-    } else {
+    } else if (warp >= Cfg::kEpiWarp0) {
         // ---------------- epilogue warps ----------------
         const int lane_grp = warp & 3;
         const int row = lane_grp * 32 + lane;
+        const int epi_tid = threadIdx.x - Cfg::kEpiWarp0 * 32;
         constexpr int kChunk = MT >= 32 ? 32 : 16;
         uint32_t item_cnt = 0;
         bool ok = true;
+        bool store_pending = false;
         for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++item_cnt) {
             const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
-            const uint32_t use = acc_use(item_cnt);
-            if (!mbar_wait(&bar_dfull[PAIR == 2 ? 0 : acc_of(item_cnt, 0)], use & 1, ST_WAIT_TMEM_FULL, w)) { ok = false; break; }
+            const int acc = acc_of(item_cnt);
+            if (!mbar_wait(&bar_dfull[acc], acc_use(item_cnt) & 1, ST_WAIT_TMEM_FULL, w)) { ok = false; break; }
             tc_fence_after();
+            const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + acc * MT;
             const int64_t n = static_cast<int64_t>(im.n_blk) * kBNW + row;
+            if (Cfg::kTmaStore && tma_store) {
+                // D^T holds [n = lane][m = column]; the output wants rows of n.  Each thread writes its
+                // column of a [128 m x 128 n] fp16 tile in shared memory (a warp writes 64 contiguous
+                // bytes per m), and one TMA store per 128 rows of m moves the tile out, clipped at M.
+                __half* tile = reinterpret_cast<__half*>(store_tile);
+#pragma unroll 1
+                for (int h = 0; h < MT / 128; ++h) {
+                    if (im.m_blk * MT + h * 128 >= M) break;
+                    if (store_pending) {                     // the previous store must have read the tile
+                        if (epi_tid == 0) tma_store_wait_read<0>();
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        store_pending = false;
+                    }
 #pragma unroll
-            for (int t = 0; t < PAIR; ++t) {
-                const int acc = acc_of(item_cnt, t);
-                const int mt0 = im.m_blk * MT * PAIR + t * MT;
-                const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + acc * MT;
-                if (mt0 < M) {
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(t_lane + h * 128 + c * 32, v);
+                        tmem_wait_ld();
+                        if (h == MT / 128 - 1 && c == 3) {   // accumulator fully read: release it
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&bar_dempty[acc]);
+                        }
 #pragma unroll
-                    for (int c = 0; c < MT / kChunk; ++c) {
+                        for (int j = 0; j < 32; ++j) tile[(c * 32 + j) * kBNW + row] = __float2half_rn(__uint_as_float(v[j]));
+                    }
+                    fence_async_smem();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (epi_tid == 0) {
+                        tma_store_2d(tmap_out, tile, im.n_blk * kBNW, im.m_blk * MT + h * 128);
+                        tma_store_commit();
+                    }
+                    store_pending = true;
+                }
+                // an item whose upper half lies beyond M never reached the release above
+                if ((MT / 128 - 1) * 128 + im.m_blk * MT >= M) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar_dempty[acc]);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < MT / kChunk; ++c) {
+                    const int m0 = im.m_blk * MT + c * kChunk;
+                    if (m0 < M) {
                         uint32_t v[kChunk];
                         if constexpr (kChunk == 32) tmem_ld32(t_lane + c * kChunk, v);
                         else                        tmem_ld16(t_lane + c * kChunk, v);
                         tmem_wait_ld();
-                        const int m0 = mt0 + c * kChunk;
                         if (splitk == 1) {
                             __half* dst = out + col_offset + n;
 #pragma unroll
@@ -334,29 +392,30 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 if (lane == 0) mbar_arrive(&bar_dempty[acc]);
             }
         }
+        if (store_pending && epi_tid == 0) tma_store_wait<0>();   // global writes complete before exit
     }
 
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 1) {
+    if (warp == 2) {
         __syncwarp();
         tmem_dealloc(tmem_base, Cfg::kTmemCols);
     }
 }
 
-#define TB200_W4_KERNEL(NAME, MT, PAIR)                                                                            \
-    extern "C" __global__ void __launch_bounds__(W4Cfg<MT, PAIR>::kThreads, 1) tb200_k_gemm_w4a16_##NAME(          \
+#define TB200_W4_KERNEL(MT)                                                                                        \
+    extern "C" __global__ void __launch_bounds__(W4Cfg<MT>::kThreads, 1) tb200_k_gemm_w4a16_m##MT(                 \
         const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_w,                  \
-        const __half* scales, __half* out, float* ws, int M, int N, int K, int gpr, int kbpg, int64_t ldo,         \
-        int64_t col_offset, int splitk, float zp1024) {                                                            \
-        gemm_w4a16_body<MT, PAIR>(&tmap_act, &tmap_w, scales, out, ws, M, N, K, gpr, kbpg, ldo, col_offset,        \
-                                  splitk, zp1024);                                                                 \
+        const __grid_constant__ CUtensorMap tmap_out, const __half* scales, __half* out, float* ws, int M, int N,  \
+        int K, int gpr, int kbpg, int64_t ldo, int64_t col_offset, int splitk, float zp1024, int tma_store) {      \
+        gemm_w4a16_body<MT>(&tmap_act, &tmap_w, &tmap_out, scales, out, ws, M, N, K, gpr, kbpg, ldo, col_offset,   \
+                            splitk, zp1024, tma_store);                                                            \
     }
-TB200_W4_KERNEL(m16, 16, 1)
-TB200_W4_KERNEL(m64, 64, 1)
-TB200_W4_KERNEL(m128, 128, 1)
-TB200_W4_KERNEL(m256, 128, 2)
+TB200_W4_KERNEL(16)
+TB200_W4_KERNEL(64)
+TB200_W4_KERNEL(128)
+TB200_W4_KERNEL(256)
 
 // out[m, col_offset + n] = fp16( ws[0][m][n] + ws[1][m][n] + ... ) — fixed order, 4 columns per thread.
 extern "C" __global__ void __launch_bounds__(256)
@@ -389,7 +448,7 @@ TB200_DEFINE_STATUS_HOOKS(gemm_w4a16)
 
 namespace {
 
-int pick_mt(int64_t m) { return m <= 16 ? 16 : (m <= 64 ? 64 : 128); }
+int pick_mt(int64_t m) { return m <= 16 ? 16 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)); }
 
 // K split for the decode-sized shapes, where there are fewer weight tiles than SMs and the kernel
 // is bound by streaming the weights: pick the split that fills whole waves of SMs best.
@@ -411,10 +470,10 @@ int pick_splitk(int64_t m, int64_t n, int64_t k) {
     return best;
 }
 
-template <int MT, int PAIR, typename Kern>
+template <int MT, typename Kern>
 int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void* out, float* ws, int64_t m, int64_t n,
               int64_t k, int64_t group, int zp, int64_t ldo, int64_t col_offset, int splitk, cudaStream_t st) {
-    using Cfg = W4Cfg<MT, PAIR>;
+    using Cfg = W4Cfg<MT>;
     static bool attr_set[64] = {false};
     int dev = 0;
     TB200_CUDA_TRY(cudaGetDevice(&dev));
@@ -422,17 +481,27 @@ int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void
         TB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         attr_set[dev] = true;
     }
-    CUtensorMap ta, tw;
+    CUtensorMap ta, tw, to;
     int rc = encode_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, m, k, k * 2, MT, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TB200_OK) return rc;
     rc = encode_tmap_2d(&tw, wp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k / 2, k / 2, kBNW, kBK / 2, CU_TENSOR_MAP_SWIZZLE_32B);
     if (rc != TB200_OK) return rc;
-    const int64_t items = (n / kBNW) * ((m + MT * PAIR - 1) / (MT * PAIR)) * splitk;
+    // TMA-store epilogue: the rank's output slice [m, n] at out + col_offset with row pitch ldo.  It needs a
+    // 16-byte aligned base and pitch; otherwise the kernel stores from registers.
+    __half* out_slice = static_cast<__half*>(out) + col_offset;
+    int tma_store = Cfg::kTmaStore && splitk == 1 && aligned16(out_slice) && (ldo % 8 == 0);
+    if (tma_store) {
+        rc = encode_tmap_2d(&to, out_slice, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, m, n, ldo * 2, 128, kBNW, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc != TB200_OK) return rc;
+    } else {
+        to = ta;   // unused by the kernel
+    }
+    const int64_t items = (n / kBNW) * ((m + MT - 1) / MT) * splitk;
     const int grid = static_cast<int>(items < num_sms() ? items : num_sms());
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(ta, tw, static_cast<const __half*>(scales), static_cast<__half*>(out), ws,
+    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(ta, tw, to, static_cast<const __half*>(scales), static_cast<__half*>(out), ws,
                                                         static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
                                                         static_cast<int>(k / group), static_cast<int>(group / kBK), ldo,
-                                                        col_offset, splitk, 1024.0f + static_cast<float>(zp));
+                                                        col_offset, splitk, 1024.0f + static_cast<float>(zp), tma_store);
     TB200_CUDA_TRY(cudaGetLastError());
     if (splitk > 1) {
         const int64_t total = m * (n / 4);
@@ -478,11 +547,10 @@ extern "C" int tb200_gemm_w4a16(const void* a, const void* wp, const void* scale
         ws = static_cast<float*>(workspace);
     }
     switch (pick_mt(m)) {
-        case 16:  return launch_w4<16, 1>(tb200_k_gemm_w4a16_m16, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
-        case 64:  return launch_w4<64, 1>(tb200_k_gemm_w4a16_m64, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
-        default:
-            if (m > 128) return launch_w4<128, 2>(tb200_k_gemm_w4a16_m256, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
-            return launch_w4<128, 1>(tb200_k_gemm_w4a16_m128, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
+        case 16:  return launch_w4<16>(tb200_k_gemm_w4a16_m16, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
+        case 64:  return launch_w4<64>(tb200_k_gemm_w4a16_m64, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
+        case 128: return launch_w4<128>(tb200_k_gemm_w4a16_m128, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
+        default:  return launch_w4<256>(tb200_k_gemm_w4a16_m256, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
     }
 }
 
