@@ -30,6 +30,8 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
+# stdout carries exactly one JSON line: keep NCCL's version banner out of it
+os.environ["NCCL_DEBUG"] = os.environ.get("TB200_NCCL_DEBUG", "WARN")
 
 ROWS, COLS = 65536, 4096
 ALG_BYTES = ROWS * COLS * 3 + ROWS * 4            # int8 in + bf16 out + fp32 scales = 805,568,512

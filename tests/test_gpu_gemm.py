@@ -125,6 +125,13 @@ def test_w4a16_matches_oracle_across_m(cuda_device, M):
     np.testing.assert_allclose(got, want, **FP16_TOL)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 128, 128), (16, 256, 384), (100, 128, 128), (128, 384, 256), (9, 256, 128)])
+def test_w4a16_short_k_fewer_blocks_than_issuers(cuda_device, M, N, K):
+    """K of only 2-6 blocks of 64: some of the MMA issuer threads get no block and must contribute zero."""
+    got, want = w4_case(M, N, K, seed=70 + M + K, device=cuda_device)
+    np.testing.assert_allclose(got, want, **FP16_TOL)
+
+
 @pytest.mark.parametrize("M", [1, 16, 128])
 def test_w4a16_config_shapes_small_m(cuda_device, M):
     got, want = w4_case(M, 14336, 4096, seed=50 + M, device=cuda_device)

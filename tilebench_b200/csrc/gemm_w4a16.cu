@@ -18,13 +18,17 @@
 // Roles:
 //   warp 0            activation TMA producer
 //   warp 1            packed-weight TMA producer
-//   warp 2            MMA issuer: four tcgen05.mma kind::f16 (A from TMEM, B from smem, K = 16 each) per
-//                     64-wide K block, then ONE tcgen05.commit: "MMAs of this K block complete" frees
-//                     the activation stage and the operand stage (same ring depth, same barrier)
-//   warp 3            idle (keeps the following warp quads aligned with the TMEM lane quarters)
-//   warps 4..11       convert warps (two groups of 4 taking alternate K blocks): thread = weight row;
+//   warps 2..5        MMA issuers (NI of them; the rest idle).  Issuer j takes K blocks with it % NI == j:
+//                     four tcgen05.mma kind::f16 (A from TMEM, B from smem, K = 16 each) into ITS OWN
+//                     accumulator, then ONE tcgen05.commit: "MMAs of this K block complete" frees the
+//                     activation stage and the operand stage (same barrier).  Small-N MMAs finish in
+//                     fewer cycles than one thread needs to issue them, so decode-sized tiles use
+//                     several issuers; private accumulators keep the summation order fixed.
+//   warps 6..7        idle (keep the following warp quads aligned with the TMEM lane quarters)
+//   warps 8..15       convert warps (two groups of 4 taking alternate K blocks): thread = weight row;
 //                     2 x LDS.128 of packed nibbles -> 64 fp16 -> tcgen05.st into an operand stage
-//   warps 12..15      epilogue: tcgen05.ld the finished accumulator, cast; for MT >= 128 transpose
+//   warps 16..19      epilogue: tcgen05.ld the finished accumulators (summed in issuer order), cast;
+//                     for MT >= 128 transpose
 //                     through a shared-memory tile and write it with one TMA store per 128 rows,
 //                     otherwise store directly (fp32 split-K partials or fp16)
 // With a K split > 1 the epilogue writes fp32 partials to the caller's workspace and a second
@@ -45,7 +49,8 @@ constexpr int kGroupN = 16;    // tile-order grouping for L2 reuse
 template <int MT> struct W4Cfg {
     static constexpr int kDQ = 2;                                // convert warp groups (alternate K blocks)
     static constexpr int kActStageBytes = MT * kBK * 2;          // one [MT x 64] fp16 activation tile
-    static constexpr int kNAcc = MT == 256 ? 1 : 2;              // accumulators (256 columns fill TMEM once)
+    static constexpr int kNI = MT <= 32 ? 4 : (MT <= 128 ? 2 : 1);   // MMA issuer threads, one accumulator each
+    static constexpr int kNAcc = MT >= 128 ? 1 : 2;              // accumulator sets (double-buffered when they fit)
     static constexpr bool kTmaStore = MT >= 128;                 // epilogue through smem + TMA store
     static constexpr int kStoreBytes = kTmaStore ? 128 * kBNW * 2 : 0;   // [128 m x 128 n] fp16 staging tile
     static constexpr int kSA = MT <= 32 ? 16 : (MT == 64 ? 12 : (MT == 128 ? 8 : 5));   // activation stages
@@ -53,12 +58,13 @@ template <int MT> struct W4Cfg {
     // TMEM operand stages, 32 columns each: as deep as the activation ring, because both are freed by
     // the same per-K-block commit and share its barrier
     static constexpr int kAStages = kSA < 8 ? kSA : 8;
-    static constexpr int kDCols = kNAcc * MT;
+    static constexpr int kDCols = kNAcc * kNI * MT;
     static constexpr int kACol0 = kDCols;
     static constexpr int kTmemNeed = kDCols + 32 * kAStages;
     static constexpr int kTmemCols = kTmemNeed <= 32 ? 32 : kTmemNeed <= 64 ? 64 : kTmemNeed <= 128 ? 128
                                      : kTmemNeed <= 256 ? 256 : 512;
-    static constexpr int kCvtWarp0 = 4;
+    static constexpr int kMmaWarp0 = 2;
+    static constexpr int kCvtWarp0 = 8;
     static constexpr int kEpiWarp0 = kCvtWarp0 + 4 * kDQ;
     static constexpr int kWarps = kEpiWarp0 + 4;
     static constexpr int kThreads = 32 * kWarps;
@@ -118,6 +124,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
     constexpr int AST = Cfg::kAStages;
     constexpr int DQ = Cfg::kDQ;
     constexpr int NACC = Cfg::kNAcc;
+    constexpr int NI = Cfg::kNI;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* act_ring = smem;
@@ -146,7 +153,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         for (int s = 0; s < SA; ++s) { mbar_init(&bar_afull[s], 1); mbar_init(&bar_done[s], 1); }
         for (int s = 0; s < SW; ++s) { mbar_init(&bar_wfull[s], 1); mbar_init(&bar_wempty[s], 4); }
         for (int s = 0; s < AST; ++s) mbar_init(&bar_ofull[s], 4);
-        for (int b = 0; b < 2; ++b) { mbar_init(&bar_dfull[b], 1); mbar_init(&bar_dempty[b], 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&bar_dfull[b], NI); mbar_init(&bar_dempty[b], 4); }
         mbar_fence_init();
         tma_prefetch_desc(tmap_act);
         tma_prefetch_desc(tmap_w);
@@ -207,19 +214,22 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 }
             }
         }
-    } else if (warp == 2) {
-        // ---------------- MMA issuer ----------------
+    } else if (warp >= Cfg::kMmaWarp0 && warp < Cfg::kMmaWarp0 + NI) {
+        // ---------------- MMA issuers ----------------
         if (lane == 0) {
+            const int me = warp - Cfg::kMmaWarp0;                    // K blocks with it % NI == me are mine
             constexpr uint32_t idesc = umma_idesc(0, 0, kBNW, MT);   // f16 x f16 -> f32, M = 128, N = MT
             uint32_t it = 0, item_cnt = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++item_cnt) {
                 const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
                 const int acc = acc_of(item_cnt);
-                const uint32_t d_tmem = tmem_base + acc * MT;
-                // the accumulator must have been drained before this item's first MMA overwrites it
+                const uint32_t d_tmem = tmem_base + (acc * NI + me) * MT;
+                // the accumulator set must have been drained before this item's first MMA overwrites it
                 if (!mbar_wait(&bar_dempty[acc], (acc_use(item_cnt) & 1) ^ 1, ST_WAIT_TMEM_EMPTY, w)) { ok = false; break; }
+                bool first = true;
                 for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
+                    if (NI > 1 && static_cast<int>(it % NI) != me) continue;
                     const int s = it % SA;
                     const int os = it % AST;
                     if (!mbar_wait(&bar_ofull[os], (it / AST) & 1, ST_WAIT_OPERAND, kb)) { ok = false; break; }
@@ -230,11 +240,12 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k) {
                         // 16 fp16 of K = 8 TMEM columns of the operand, 32 bytes of the swizzled smem row
-                        umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, (kb > im.kb0 || k > 0) ? 1u : 0u);
+                        umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
                     }
+                    first = false;
                     tc_commit(&bar_done[s]);
                 }
-                if (ok) tc_commit(&bar_dfull[acc]);
+                if (ok) tc_commit(&bar_dfull[acc]);   // one arrival per issuer; every issuer had >= 1 K block
             }
         }
     } else if (warp >= Cfg::kCvtWarp0 && warp < Cfg::kEpiWarp0) {
@@ -315,16 +326,41 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         const int row = lane_grp * 32 + lane;
         const int epi_tid = threadIdx.x - Cfg::kEpiWarp0 * 32;
         constexpr int kChunk = MT >= 32 ? 32 : 16;
-        uint32_t item_cnt = 0;
+        uint32_t item_cnt = 0, it0 = 0;
         bool ok = true;
         bool store_pending = false;
         for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++item_cnt) {
             const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
             const int acc = acc_of(item_cnt);
+            // issuer i wrote its accumulator in this item iff one of the item's K blocks (global
+            // numbers it0 .. it0 + len - 1) is congruent to i modulo NI
+            const uint32_t len = static_cast<uint32_t>(im.kb1 - im.kb0);
+            const uint32_t first_issuer = it0 % NI;
+            it0 += len;
+            auto issuer_active = [&](int i) { return len >= static_cast<uint32_t>(NI) || ((i + NI - first_issuer) % NI) < len; };
             if (!mbar_wait(&bar_dfull[acc], acc_use(item_cnt) & 1, ST_WAIT_TMEM_FULL, w)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + acc * MT;
+            const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + acc * NI * MT;
             const int64_t n = static_cast<int64_t>(im.n_blk) * kBNW + row;
+            // v[] = sum over the issuers' private accumulators, always in issuer order
+            auto load_sum = [&](uint32_t col, auto& v) {
+                constexpr int W = sizeof(v) / sizeof(v[0]);
+                if constexpr (W == 32) tmem_ld32(t_lane + col, v); else tmem_ld16(t_lane + col, v);
+                tmem_wait_ld();
+                if (NI > 1 && !issuer_active(0)) {
+#pragma unroll
+                    for (int j = 0; j < W; ++j) v[j] = 0u;
+                }
+#pragma unroll
+                for (int i = 1; i < NI; ++i) {
+                    if (!issuer_active(i)) continue;
+                    uint32_t u[W];
+                    if constexpr (W == 32) tmem_ld32(t_lane + i * MT + col, u); else tmem_ld16(t_lane + i * MT + col, u);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < W; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
+                }
+            };
             if (Cfg::kTmaStore && tma_store) {
                 // D^T holds [n = lane][m = column]; the output wants rows of n.  Each thread writes its
                 // column of a [128 m x 128 n] fp16 tile in shared memory (a warp writes 64 contiguous
@@ -341,8 +377,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t v[32];
-                        tmem_ld32(t_lane + h * 128 + c * 32, v);
-                        tmem_wait_ld();
+                        load_sum(h * 128 + c * 32, v);
                         if (h == MT / 128 - 1 && c == 3) {   // accumulator fully read: release it
                             tc_fence_before();
                             __syncwarp();
@@ -371,9 +406,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                     const int m0 = im.m_blk * MT + c * kChunk;
                     if (m0 < M) {
                         uint32_t v[kChunk];
-                        if constexpr (kChunk == 32) tmem_ld32(t_lane + c * kChunk, v);
-                        else                        tmem_ld16(t_lane + c * kChunk, v);
-                        tmem_wait_ld();
+                        load_sum(c * kChunk, v);
                         if (splitk == 1) {
                             __half* dst = out + col_offset + n;
 #pragma unroll
