@@ -30,8 +30,11 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
-# stdout carries exactly one JSON line: keep NCCL's version banner out of it
-os.environ["NCCL_DEBUG"] = os.environ.get("TB200_NCCL_DEBUG", "WARN")
+# stdout carries exactly one JSON line: NCCL prints its version banner there at NCCL_DEBUG=VERSION and
+# above, so the variable is cleared unless TB200_NCCL_DEBUG asks for a level
+os.environ.pop("NCCL_DEBUG", None)
+if os.environ.get("TB200_NCCL_DEBUG"):
+    os.environ["NCCL_DEBUG"] = os.environ["TB200_NCCL_DEBUG"]
 
 ROWS, COLS = 65536, 4096
 ALG_BYTES = ROWS * COLS * 3 + ROWS * 4            # int8 in + bf16 out + fp32 scales = 805,568,512
@@ -271,7 +274,7 @@ def sections(torch, dev, peaks, world, rank, steps, warmup):
     a = torch.randn(M, K, device=dev, generator=torch.Generator(device=dev).manual_seed(99)).half()   # replicated
     wp = torch.randint(0, 256, (n_local, K // 2), dtype=torch.uint8, device=dev, generator=gen)
     sc = (torch.randn(n_local, K // 128, device=dev, generator=gen).abs() * 0.01 + 1e-3).half()
-    for gather in (False, True):
+    for gather in ((False, "nccl", "fused") if world > 1 else (False,)):
         def call():
             return npart.gemm_w4a16_partitioned(a, wp, sc, 128, 8, gather=gather)
         for _ in range(warmup):
@@ -284,7 +287,7 @@ def sections(torch, dev, peaks, world, rank, steps, warmup):
             t = torch.tensor([ms], device=dev)
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
             ms = float(t.item())
-        r = tensor_row(f"gemm_w4a16_npart M=4096 K=8192 N=57344 world={world} gather={int(gather)}", 2 * M * N * K, ms,
+        r = tensor_row(f"gemm_w4a16_npart M=4096 K=8192 N=57344 world={world} gather={gather or 'none'}", 2 * M * N * K, ms,
                        peaks["bf16_tflops"] * world, f"{world} x bf16 cuBLAS burst ({peaks['source']})",
                        note="aggregate over ranks, max-over-ranks time; output allocation included")
         out.append(r)

@@ -121,9 +121,24 @@ int    tb200_gemm_w4a16(const void* a, const void* wp, const void* scales, void*
                         void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * N-partitioned W4A16 GEMM fused with the all-gather of its column slices (config `gemm_w4a16_npart`;
+ * the reference has no multi-GPU path).  Rank `rank` of `world` owns weight rows
+ * [rank * n_local, (rank + 1) * n_local); out_ptrs[r] is rank r's full output [m, ldo] (fp16, ldo >= world *
+ * n_local), peer-mapped into this process for r != rank (symmetric memory / CUDA IPC).  The epilogue stores
+ * every finished tile into columns [rank * n_local, ...) of ALL `world` buffers — its own by TMA store, the
+ * others by 128-bit peer stores over NVLink — so the transfer overlaps the main loop.  Needs m > 64 and
+ * 16-byte aligned slices (TB200_ERR_UNSUPPORTED otherwise: gather with NCCL instead).  Callers must put a
+ * cross-rank barrier between this call and any read of the gathered buffer.  out_ptrs is a HOST array.
+ */
+int tb200_gemm_w4a16_gather(const void* a, const void* wp_local, const void* scales_local,
+                            void* const* out_ptrs, int world, int rank, int64_t m, int64_t n_local, int64_t k,
+                            int64_t group, int zero_point, int64_t ldo, void* stream);
+
+/*
  * W4A16 GEMM for callers that cannot allocate device memory.  No counterpart in the reference.
  *
- * tb200_gemm_w4a16 asks its caller for a split-K workspace when m is decode-sized.  Some callers have
+ * tb200_gemm_w4a16 asks its caller for a split-K workspace when m is small (17..64 rows; fewer rows take a
+ * streaming kernel that needs none).  Some callers have
  * no way to provide one: a plugin running inside a host process that has handed all device memory to its
  * own pool, or code invoked where cudaMalloc is not permitted.  This variant computes the same result
  * with the partial sums kept in a fixed array of TB200_W4A16_STATIC_SCRATCH_BYTES that is part of the
@@ -138,7 +153,7 @@ int    tb200_gemm_w4a16(const void* a, const void* wp, const void* scales, void*
  *     partial sum a call reads is written by that same call first, so nothing has to be cleared; but two
  *     calls that overlap on the GPU (different streams, or concurrent graphs) race on it.  Serialise them.
  */
-#define TB200_W4A16_STATIC_SCRATCH_BYTES (8u << 20)
+#define TB200_W4A16_STATIC_SCRATCH_BYTES (16u << 20)
 size_t tb200_gemm_w4a16_static_scratch_bytes(void);
 int    tb200_gemm_w4a16_static(const void* a, const void* wp, const void* scales, void* out,
                                int64_t m, int64_t n, int64_t k, int64_t group, int zero_point,

@@ -101,11 +101,13 @@ def w4_case(M, N, K, seed, device, group=128):
     return out.float().cpu().numpy(), want.astype(np.float32)
 
 
-def test_w4a16_one_hot_rows_read_out_weight_columns_exactly(cuda_device):
+@pytest.mark.parametrize("M", [128, 16])
+def test_w4a16_one_hot_rows_read_out_weight_columns_exactly(cuda_device, M):
     """Activation row i is one-hot at column k_i: the output row must be the dequantised weight
-    column k_i, bit for bit — pins nibble order, group scales, TMEM operand layout and K order."""
+    column k_i, bit for bit — pins nibble order, group scales, operand layout and K order
+    (M = 128: tensor-memory GEMM; M = 16: the streaming mma.sync kernel and its permuted K order)."""
     from tilebench_b200.benchmarks.operators.gemm_w4a16 import impl_cuda
-    N, K, M = 256, 512, 128
+    N, K = 256, 512
     wp, sc = tensors.make_int4_group_weights(N, K, 128, seed=3)
     ks = torch.randperm(K, generator=torch.Generator().manual_seed(1))[:M]
     a = torch.zeros(M, K, dtype=torch.float16)
@@ -119,7 +121,7 @@ def test_w4a16_one_hot_rows_read_out_weight_columns_exactly(cuda_device):
     assert np.array_equal(out.cpu().numpy().view(np.uint16), np.ascontiguousarray(want).view(np.uint16))
 
 
-@pytest.mark.parametrize("M", [1, 3, 16, 17, 64, 127, 128, 129, 300])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 24, 64, 127, 128, 129, 300])
 def test_w4a16_matches_oracle_across_m(cuda_device, M):
     got, want = w4_case(M, 512, 1024, seed=40 + M, device=cuda_device)
     np.testing.assert_allclose(got, want, **FP16_TOL)
@@ -173,9 +175,9 @@ def test_w4a16_column_offset_writes_only_its_slice(cuda_device, M):
 
 def test_w4a16_workspace_too_small_is_an_error(cuda_device):
     ext = native.load()
-    a, wp, sc, group, zp = tensors.generate_gemm_w4a16_inputs(1, 4096, 14336, device=cuda_device, seed=9)
-    if ext.gemm_w4a16_workspace_bytes(1, 14336, 4096) == 0:
+    a, wp, sc, group, zp = tensors.generate_gemm_w4a16_inputs(24, 4096, 14336, device=cuda_device, seed=9)
+    if ext.gemm_w4a16_workspace_bytes(24, 14336, 4096) == 0:
         pytest.skip("no split-K for this shape")
-    out = torch.empty(1, 14336, dtype=torch.float16, device=cuda_device)
+    out = torch.empty(24, 14336, dtype=torch.float16, device=cuda_device)
     with pytest.raises(ValueError):
         ext.gemm_w4a16(a, wp, sc, out, group, zp, 0, None)

@@ -44,12 +44,13 @@ def run_pair(lib, dev, m, n, k, seed):
 
 def test_static_scratch_matches_workspace_entry_point_twice(cuda_device):
     lib = native.capi()
-    assert lib.tb200_gemm_w4a16_static_scratch_bytes() == 8 << 20
+    assert lib.tb200_gemm_w4a16_static_scratch_bytes() == 16 << 20
     native.clear_device_status()
-    # decode-sized m on the benchmark's weight shape: split-K, so the built-in array is really used
-    for seed, m in ((101, 16), (202, 1)):
+    # small m above the streaming kernel's range on the benchmark's weight shape: the tensor-memory
+    # GEMM splits K there, so the built-in array is really used
+    for seed, m in ((101, 24), (202, 17)):
         need, got, ref = run_pair(lib, cuda_device, m, 14336, 4096, seed)
-        assert 0 < need <= 8 << 20
+        assert 0 < need <= 16 << 20
         np.testing.assert_allclose(got.float().cpu().numpy(), ref.float().cpu().numpy(), **FP16_TOL)
     assert native.device_status()[0] == 0
 
@@ -60,8 +61,8 @@ def test_static_entry_point_without_scratch_and_over_the_limit(cuda_device):
     assert need == 0
     np.testing.assert_allclose(got.float().cpu().numpy(), ref.float().cpu().numpy(), **FP16_TOL)
     # a shape whose partial sums do not fit is refused with a message, not run
-    m, k = 16, 4096
-    n = next((c for c in (98304, 81920, 114688, 49152) if lib.tb200_gemm_w4a16_workspace_bytes(m, c, k) > 8 << 20), None)
+    m, k = 64, 4096
+    n = next((c for c in (14336, 28672, 57344, 8192) if lib.tb200_gemm_w4a16_workspace_bytes(m, c, k) > 16 << 20), None)
     if n is None:
         pytest.skip("no probe shape exceeds the built-in array on this device")
     t = torch.zeros(16, dtype=torch.uint8, device=cuda_device)

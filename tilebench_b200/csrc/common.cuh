@@ -266,6 +266,10 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
 }
 #endif  // __CUDACC__
 
+// ---- host: launcher of the decode-sized W4A16 kernel (gemv_w4a16.cu), used by tb200_gemm_w4a16 -----
+int launch_gemv_w4a16(const void* a, const void* wp, const void* scales, void* out, int64_t m, int64_t n, int64_t k,
+                      int64_t group, int zero_point, int64_t ldo, int64_t col_offset, cudaStream_t st);
+
 // ---- host: TMA descriptor encoding through the driver entry point (no libcuda link) ----------
 // 2-D row-major tensor [rows, cols] of elem_bytes-wide elements with row pitch `pitch_bytes`,
 // box [box_rows, box_cols], given swizzle.  Returns TB200_OK or an error code.

@@ -14,13 +14,17 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
 
-// Persistent launch: enough CTAs to fill every SM's thread slots, never more than the work needs.
+// Persistent launch: at most one full wave of CTAs (every SM's thread slots), and — when the work
+// needs several passes — a grid that gives every CTA the same number of passes, so no SM idles
+// while a few CTAs run one pass more.
 inline unsigned grid_for(uint64_t work_items, int threads, int unroll) {
     uint64_t per_cta = static_cast<uint64_t>(threads) * unroll;
     uint64_t need = (work_items + per_cta - 1) / per_cta;
     uint64_t cap = static_cast<uint64_t>(num_sms()) * (2048 / threads);
     if (need < 1) need = 1;
-    return static_cast<unsigned>(need < cap ? need : cap);
+    if (need <= cap) return static_cast<unsigned>(need);
+    uint64_t passes = (need + cap - 1) / cap;
+    return static_cast<unsigned>((need + passes - 1) / passes);
 }
 
 // Two nibbles of one byte -> half2 (low nibble first), exact:  h = 0x6400 | q  is 1024 + q.
@@ -38,10 +42,11 @@ __device__ __forceinline__ __half2 nib_pair_to_half2(uint32_t lo_src, uint32_t h
 using namespace tb200;
 
 // out[r, c] = fp16((q - zp) * s[r, c/group]);  one thread-chunk = 4 packed bytes = 8 outputs.
-extern "C" __global__ void __launch_bounds__(kThreads)
-tb200_k_dequant_int4_group(const uint32_t* __restrict__ wp, const __half* __restrict__ scales,
-                           __half* __restrict__ out, uint32_t chunks_per_row, uint32_t group_chunks,
-                           uint32_t groups_per_row, uint64_t total_chunks, int64_t ldo, float zp_plus_1024) {
+template <int kUnroll>
+__device__ __forceinline__ void dequant_int4_group_body(const uint32_t* __restrict__ wp, const __half* __restrict__ scales,
+                                                        __half* __restrict__ out, uint32_t chunks_per_row,
+                                                        uint32_t group_chunks, uint32_t groups_per_row,
+                                                        uint64_t total_chunks, int64_t ldo, float zp_plus_1024) {
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
     const __half2 bias = __float2half2_rn(zp_plus_1024);  // 1024 + zero_point, exact for 0..15
     for (uint64_t base = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; base < total_chunks;
@@ -78,6 +83,19 @@ tb200_k_dequant_int4_group(const uint32_t* __restrict__ wp, const __half* __rest
             }
         }
     }
+}
+
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_dequant_int4_group(const uint32_t* wp, const __half* scales, __half* out, uint32_t cpr, uint32_t gc,
+                           uint32_t gpr, uint64_t total, int64_t ldo, float zp1024) {
+    dequant_int4_group_body<4>(wp, scales, out, cpr, gc, gpr, total, ldo, zp1024);
+}
+// Same kernel with eight chunks in flight per thread: used when that lets one wave of CTAs cover the
+// whole matrix in a single pass (mid-sized matrices, where a second pass would mostly be latency).
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_dequant_int4_group_u8(const uint32_t* wp, const __half* scales, __half* out, uint32_t cpr, uint32_t gc,
+                              uint32_t gpr, uint64_t total, int64_t ldo, float zp1024) {
+    dequant_int4_group_body<8>(wp, scales, out, cpr, gc, gpr, total, ldo, zp1024);
 }
 
 // Any even k, any group that divides k: one output element per thread.
@@ -327,8 +345,12 @@ extern "C" int tb200_dequant_int4_group(const void* wp, const void* scales, void
                      ((reinterpret_cast<uintptr_t>(wp) & 3u) == 0) && (k / 8 < (1ll << 32));
     if (vec) {
         uint64_t total = static_cast<uint64_t>(n) * static_cast<uint64_t>(k / 8);
-        unsigned grid = grid_for(total, kThreads, kUnroll);
-        tb200_k_dequant_int4_group<<<grid, kThreads, 0, st>>>(
+        const uint64_t cap = static_cast<uint64_t>(num_sms()) * (2048 / kThreads);
+        const uint64_t need4 = (total + kThreads * 4 - 1) / (kThreads * 4), need8 = (total + kThreads * 8 - 1) / (kThreads * 8);
+        const bool one_pass_u8 = need4 > cap && need8 <= cap;
+        unsigned grid = grid_for(total, kThreads, one_pass_u8 ? 8 : 4);
+        auto kern = one_pass_u8 ? tb200_k_dequant_int4_group_u8 : tb200_k_dequant_int4_group;
+        kern<<<grid, kThreads, 0, st>>>(
             static_cast<const uint32_t*>(wp), static_cast<const __half*>(scales), static_cast<__half*>(out),
             static_cast<uint32_t>(k / 8), static_cast<uint32_t>(group / 8), static_cast<uint32_t>(k / group), total,
             ldo, 1024.0f + static_cast<float>(zero_point));

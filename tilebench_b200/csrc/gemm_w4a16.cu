@@ -78,6 +78,14 @@ template <int MT> struct W4Cfg {
     static_assert(kSmemBytes <= 232448, "over the 227 KB shared-memory limit");
 };
 
+// Output buffers of the other ranks of an N-partitioned GEMM (already offset to this rank's column
+// slice): the epilogue stores every finished tile there too, so the all-gather rides on the GEMM.
+constexpr int kMaxPeers = 7;
+struct PeerOut {
+    int count;
+    __half* base[kMaxPeers];
+};
+
 struct Item { int n_blk, m_blk, kb0, kb1, ks; };
 // tiles_m counts activation tiles of MT rows.
 __device__ __forceinline__ Item make_item(int w, int tiles_n, int tiles_m, int splitk, int KB) {
@@ -117,7 +125,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                                                 const __half* __restrict__ scales, __half* __restrict__ out,
                                                 float* __restrict__ ws, int M, int N, int K, int groups_per_row,
                                                 int kb_per_group, int64_t ldo, int64_t col_offset, int splitk,
-                                                float zp_plus_1024, int tma_store) {
+                                                float zp_plus_1024, int tma_store, const PeerOut& peers) {
     using Cfg = W4Cfg<MT>;
     constexpr int SA = Cfg::kSA;
     constexpr int SW = Cfg::kSW;
@@ -393,6 +401,19 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                         tma_store_commit();
                     }
                     store_pending = true;
+                    if (peers.count > 0) {
+                        // the same tile to every other rank: 16 threads write one 256-byte row, 128-bit stores
+                        const int row0 = im.m_blk * MT + h * 128;
+                        const int rows_valid = min(128, M - row0);
+                        for (int p = 0; p < peers.count; ++p) {
+                            __half* dst = peers.base[p] + static_cast<int64_t>(row0) * ldo + im.n_blk * kBNW;
+                            for (int idx = epi_tid; idx < rows_valid * 16; idx += 128) {
+                                const int r = idx >> 4, c = idx & 15;
+                                const uint4 v = *reinterpret_cast<const uint4*>(tile + r * kBNW + c * 8);
+                                *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * ldo + c * 8) = v;
+                            }
+                        }
+                    }
                 }
                 // an item whose upper half lies beyond M never reached the release above
                 if ((MT / 128 - 1) * 128 + im.m_blk * MT >= M) {
@@ -426,6 +447,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
             }
         }
         if (store_pending && epi_tid == 0) tma_store_wait<0>();   // global writes complete before exit
+        if (peers.count > 0) __threadfence_system();              // peer stores visible beyond this GPU
     }
 
     tc_fence_before();
@@ -441,9 +463,10 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
     extern "C" __global__ void __launch_bounds__(W4Cfg<MT>::kThreads, 1) tb200_k_gemm_w4a16_m##MT(                 \
         const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_w,                  \
         const __grid_constant__ CUtensorMap tmap_out, const __half* scales, __half* out, float* ws, int M, int N,  \
-        int K, int gpr, int kbpg, int64_t ldo, int64_t col_offset, int splitk, float zp1024, int tma_store) {      \
+        int K, int gpr, int kbpg, int64_t ldo, int64_t col_offset, int splitk, float zp1024, int tma_store,        \
+        const PeerOut peers) {                                                                                     \
         gemm_w4a16_body<MT>(&tmap_act, &tmap_w, &tmap_out, scales, out, ws, M, N, K, gpr, kbpg, ldo, col_offset,   \
-                            splitk, zp1024, tma_store);                                                            \
+                            splitk, zp1024, tma_store, peers);                                                     \
     }
 TB200_W4_KERNEL(16)
 TB200_W4_KERNEL(64)
@@ -483,11 +506,16 @@ namespace {
 
 int pick_mt(int64_t m) { return m <= 16 ? 16 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)); }
 
-// K split for the decode-sized shapes, where there are fewer weight tiles than SMs and the kernel
-// is bound by streaming the weights: pick the split that fills whole waves of SMs best.
+// Shapes of at most kGemvMaxM activation rows go to the streaming mma.sync kernel (gemv_w4a16.cu).
+constexpr int64_t kGemvMaxM = 16;
+bool use_gemv(int64_t m, int64_t group) { return m <= kGemvMaxM && group % 128 == 0; }
+
+// K split for the small-tile shapes (17 <= m <= 64), where there are fewer weight tiles than SMs:
+// pick the split that fills whole waves of SMs best.  Every split keeps at least 4 K blocks, which
+// also guarantees each MMA issuer thread its own block.
 int pick_splitk(int64_t m, int64_t n, int64_t k) {
     const int mt = pick_mt(m);
-    if (mt > 16) return 1;
+    if (mt > 64) return 1;
     const int64_t tiles = (n / kBNW) * ((m + mt - 1) / mt);
     const int sms = num_sms();
     const int64_t KB = k / kBK;
@@ -505,7 +533,8 @@ int pick_splitk(int64_t m, int64_t n, int64_t k) {
 
 template <int MT, typename Kern>
 int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void* out, float* ws, int64_t m, int64_t n,
-              int64_t k, int64_t group, int zp, int64_t ldo, int64_t col_offset, int splitk, cudaStream_t st) {
+              int64_t k, int64_t group, int zp, int64_t ldo, int64_t col_offset, int splitk, const PeerOut& peers,
+              cudaStream_t st) {
     using Cfg = W4Cfg<MT>;
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -523,6 +552,8 @@ int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void
     // 16-byte aligned base and pitch; otherwise the kernel stores from registers.
     __half* out_slice = static_cast<__half*>(out) + col_offset;
     int tma_store = Cfg::kTmaStore && splitk == 1 && aligned16(out_slice) && (ldo % 8 == 0);
+    if (peers.count > 0 && !tma_store)
+        return fail(TB200_ERR_UNSUPPORTED, "gemm_w4a16_gather: the fused gather needs m > 64 and 16-byte aligned output slices");
     if (tma_store) {
         rc = encode_tmap_2d(&to, out_slice, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, m, n, ldo * 2, 128, kBNW, CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc != TB200_OK) return rc;
@@ -534,7 +565,7 @@ int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void
     kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(ta, tw, to, static_cast<const __half*>(scales), static_cast<__half*>(out), ws,
                                                         static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
                                                         static_cast<int>(k / group), static_cast<int>(group / kBK), ldo,
-                                                        col_offset, splitk, 1024.0f + static_cast<float>(zp), tma_store);
+                                                        col_offset, splitk, 1024.0f + static_cast<float>(zp), tma_store, peers);
     TB200_CUDA_TRY(cudaGetLastError());
     if (splitk > 1) {
         const int64_t total = m * (n / 4);
@@ -552,13 +583,15 @@ int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void
 
 extern "C" size_t tb200_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (m <= 0 || n <= 0 || k <= 0 || n % kBNW != 0 || k % 128 != 0) return 0;
+    if (m <= kGemvMaxM) return 0;                 // streaming kernel: no split-K scratch
     const int s = pick_splitk(m, n, k);
     return s > 1 ? static_cast<size_t>(s) * m * n * sizeof(float) : 0;
 }
 
-extern "C" int tb200_gemm_w4a16(const void* a, const void* wp, const void* scales, void* out, int64_t m, int64_t n,
-                                int64_t k, int64_t group, int zero_point, int64_t ldo, int64_t col_offset,
-                                void* workspace, size_t workspace_bytes, void* stream) {
+namespace {
+int gemm_w4a16_impl(const void* a, const void* wp, const void* scales, void* out, int64_t m, int64_t n, int64_t k,
+                    int64_t group, int zero_point, int64_t ldo, int64_t col_offset, void* workspace,
+                    size_t workspace_bytes, const PeerOut& peers, void* stream) {
     clear_error();
     if (!a || !wp || !scales || !out) return fail(TB200_ERR_ARG, "gemm_w4a16: null pointer");
     if (m <= 0 || n <= 0 || k <= 0) return fail(TB200_ERR_ARG, "gemm_w4a16: non-positive size m=%lld n=%lld k=%lld", (long long)m, (long long)n, (long long)k);
@@ -570,6 +603,7 @@ extern "C" int tb200_gemm_w4a16(const void* a, const void* wp, const void* scale
     if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) return fail(TB200_ERR_UNSUPPORTED, "gemm_w4a16: dimension too large");
     if (!aligned16(a) || !aligned16(wp)) return fail(TB200_ERR_ALIGN, "gemm_w4a16: a and wp must be 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (use_gemv(m, group) && peers.count == 0) return launch_gemv_w4a16(a, wp, scales, out, m, n, k, group, zero_point, ldo, col_offset, st);
     const int splitk = pick_splitk(m, n, k);
     float* ws = nullptr;
     if (splitk > 1) {
@@ -580,11 +614,40 @@ extern "C" int tb200_gemm_w4a16(const void* a, const void* wp, const void* scale
         ws = static_cast<float*>(workspace);
     }
     switch (pick_mt(m)) {
-        case 16:  return launch_w4<16>(tb200_k_gemm_w4a16_m16, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
-        case 64:  return launch_w4<64>(tb200_k_gemm_w4a16_m64, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
-        case 128: return launch_w4<128>(tb200_k_gemm_w4a16_m128, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
-        default:  return launch_w4<256>(tb200_k_gemm_w4a16_m256, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, st);
+        case 16:  return launch_w4<16>(tb200_k_gemm_w4a16_m16, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, peers, st);
+        case 64:  return launch_w4<64>(tb200_k_gemm_w4a16_m64, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, peers, st);
+        case 128: return launch_w4<128>(tb200_k_gemm_w4a16_m128, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, peers, st);
+        default:  return launch_w4<256>(tb200_k_gemm_w4a16_m256, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, peers, st);
     }
+}
+}  // namespace
+
+extern "C" int tb200_gemm_w4a16(const void* a, const void* wp, const void* scales, void* out, int64_t m, int64_t n,
+                                int64_t k, int64_t group, int zero_point, int64_t ldo, int64_t col_offset,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+    return gemm_w4a16_impl(a, wp, scales, out, m, n, k, group, zero_point, ldo, col_offset, workspace, workspace_bytes,
+                           PeerOut{}, stream);
+}
+
+extern "C" int tb200_gemm_w4a16_gather(const void* a, const void* wp_local, const void* scales_local,
+                                       void* const* out_ptrs, int world, int rank, int64_t m, int64_t n_local, int64_t k,
+                                       int64_t group, int zero_point, int64_t ldo, void* stream) {
+    clear_error();
+    if (!out_ptrs || world < 1 || world > kMaxPeers + 1 || rank < 0 || rank >= world)
+        return fail(TB200_ERR_ARG, "gemm_w4a16_gather: bad world=%d rank=%d (1..%d ranks)", world, rank, kMaxPeers + 1);
+    if (ldo < static_cast<int64_t>(world) * n_local)
+        return fail(TB200_ERR_ARG, "gemm_w4a16_gather: ldo=%lld < world*n_local=%lld", (long long)ldo, (long long)(world * n_local));
+    const int64_t col_offset = static_cast<int64_t>(rank) * n_local;
+    PeerOut peers{};
+    for (int r = 0; r < world; ++r) {
+        if (!out_ptrs[r]) return fail(TB200_ERR_ARG, "gemm_w4a16_gather: null output pointer for rank %d", r);
+        if (r == rank) continue;
+        __half* base = static_cast<__half*>(out_ptrs[r]) + col_offset;
+        if (!aligned16(base)) return fail(TB200_ERR_ALIGN, "gemm_w4a16_gather: peer output slices must be 16-byte aligned");
+        peers.base[peers.count++] = base;
+    }
+    return gemm_w4a16_impl(a, wp_local, scales_local, out_ptrs[rank], m, n_local, k, group, zero_point, ldo, col_offset,
+                           nullptr, 0, peers, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -132,6 +132,24 @@ void gemm_w4a16(const torch::Tensor& a, const torch::Tensor& wp, const torch::Te
              "tb200_gemm_w4a16");
 }
 
+// Fused GEMM + all-gather: out_ptrs[r] is the address of rank r's full [m, ldo] fp16 output (peer-mapped).
+void gemm_w4a16_gather(const torch::Tensor& a, const torch::Tensor& wp, const torch::Tensor& scales,
+                       const std::vector<int64_t>& out_ptrs, int64_t rank, int64_t ldo, int64_t group,
+                       int64_t zero_point) {
+    check_cuda(a, "a", torch::kFloat16);
+    check_cuda(wp, "wp", torch::kUInt8);
+    check_cuda(scales, "scales", torch::kFloat16);
+    TORCH_CHECK(a.dim() == 2 && wp.dim() == 2 && a.size(1) == wp.size(1) * 2, "a [m,k], wp [n_local,k/2]");
+    const int64_t m = a.size(0), k = a.size(1), n_local = wp.size(0);
+    TORCH_CHECK(group > 0 && scales.dim() == 2 && scales.size(0) == n_local && scales.size(1) * group == k, "scales must be [n_local, k/group]");
+    std::vector<void*> ptrs;
+    for (int64_t p : out_ptrs) ptrs.push_back(reinterpret_cast<void*>(static_cast<uintptr_t>(p)));
+    c10::cuda::CUDAGuard guard(a.device());
+    check_rc(tb200_gemm_w4a16_gather(a.data_ptr(), wp.data_ptr(), scales.data_ptr(), ptrs.data(), static_cast<int>(ptrs.size()),
+                                     static_cast<int>(rank), m, n_local, k, group, static_cast<int>(zero_point), ldo, stream_of(a)),
+             "tb200_gemm_w4a16_gather");
+}
+
 py::tuple device_status() {
     int code = 0, detail = 0;
     check_rc(tb200_device_status(&code, &detail), "tb200_device_status");
@@ -153,6 +171,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_fp8_blockscaled", &gemm_fp8_blockscaled);
     m.def("gemm_w4a16_workspace_bytes", &gemm_w4a16_workspace_bytes);
     m.def("gemm_w4a16", &gemm_w4a16);
+    m.def("gemm_w4a16_gather", &gemm_w4a16_gather);
     m.def("device_status", &device_status);
     m.def("clear_device_status", &clear_device_status);
 }

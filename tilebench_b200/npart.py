@@ -4,8 +4,13 @@ the plumbing, no data-path collective unless a replicated result is asked for.
   partition(n, world, rank)        rows [lo, hi) of the weight a rank owns (128-row tiles never straddle)
   gemm_w4a16_partitioned(...)      local GEMM on the rank's slice; gather=True all-gathers the column
                                    slices into [M, N] on every rank
-The gather uses one NCCL all-gather of the contiguous per-rank slices [M, N/G] into a staging
-buffer [G, M, N/G], followed by one interleave pass into row-major [M, N].
+Two gathers:
+  "fused"  the GEMM epilogue stores every finished tile into the output buffer of EVERY rank
+           (tb200_gemm_w4a16_gather: TMA store locally, 128-bit peer stores over NVLink), so the transfer
+           overlaps the main loop.  The [M, N] output lives in a symmetric-memory buffer that is
+           allocated once per shape and reused (peers must have it mapped before the call).
+  "nccl"   one NCCL all-gather of the contiguous per-rank slices [M, N/G] into a staging buffer
+           [G, M, N/G], then one interleave pass into a fresh row-major [M, N].
 `partitioned_reference` runs the same partition -> local op -> gather path with any local function
 and any backend (gloo on CPU), which is how the host logic is tested without GPUs.
 """
@@ -51,13 +56,46 @@ def all_gather_columns(local: torch.Tensor, group=None) -> torch.Tensor:
     return interleave_slices(staging)
 
 
-def gemm_w4a16_partitioned(a, wp_local, scales_local, group_size: int = 128, zp: int = 8, gather: bool = True,
+_symm_cache: dict = {}
+
+
+def symmetric_output(m: int, n: int, device) -> tuple:
+    """(tensor [m, n] fp16, handle) of a symmetric-memory buffer every rank has mapped; cached per shape."""
+    import torch.distributed._symmetric_memory as symm_mem
+    key = (m, n, str(device))
+    if key not in _symm_cache:
+        t = symm_mem.empty((m, n), dtype=torch.float16, device=device)
+        hdl = symm_mem.rendezvous(t, dist.group.WORLD)
+        _symm_cache[key] = (t, hdl)
+    return _symm_cache[key]
+
+
+def gemm_w4a16_fused_gather(a, wp_local, scales_local, group_size: int = 128, zp: int = 8):
+    """out = a @ dequant(wp)^T on every rank, the all-gather done by the GEMM's epilogue (see module doc).
+    Returns the shared symmetric buffer: its contents are overwritten by the next call."""
+    from tilebench_b200 import native
+    ext = native.load()
+    world, rank = world_and_rank()
+    m, k = a.shape
+    n = wp_local.shape[0] * world
+    out, hdl = symmetric_output(m, n, a.device)
+    hdl.barrier()            # every rank is done reading the previous contents
+    ext.gemm_w4a16_gather(a, wp_local.contiguous(), scales_local.contiguous(), [int(p) for p in hdl.buffer_ptrs], rank, n,
+                          int(group_size), int(zp))
+    hdl.barrier()            # every rank's stores have landed
+    return out
+
+
+def gemm_w4a16_partitioned(a, wp_local, scales_local, group_size: int = 128, zp: int = 8, gather=True,
                            workspace=None):
-    """This rank's slice of out = a @ dequant(wp)^T; the full [M, N] when gather=True."""
+    """This rank's slice of out = a @ dequant(wp)^T, or the full [M, N]: gather=True / "nccl" gathers with
+    NCCL into a fresh tensor, gather="fused" uses the epilogue peer stores (m > 64, world > 1)."""
     from tilebench_b200 import native
     ext = native.load()
     m, k = a.shape
     n_local = wp_local.shape[0]
+    if gather == "fused" and world_and_rank()[0] > 1 and m > 64:
+        return gemm_w4a16_fused_gather(a, wp_local, scales_local, group_size, zp)
     out_local = torch.empty((m, n_local), dtype=torch.float16, device=a.device)
     ws_bytes = ext.gemm_w4a16_workspace_bytes(m, n_local, k)
     if ws_bytes and workspace is None:
