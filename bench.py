@@ -139,7 +139,7 @@ def run_reference(args):
     dt = (time.perf_counter() - t0) / args.steps
     value = sample_bytes / dt / 1e9
     sample = f"{sample_rows} of {ROWS} rows per step ({sample_bytes} algorithmic bytes), torch CPU, {cores} threads"
-    print(json.dumps({
+    print(file=args.out, *[json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -147,7 +147,7 @@ def run_reference(args):
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-    }))
+    })])
 
 
 # ------------------------------------------------------------------------------------------------
@@ -430,10 +430,19 @@ def run_ours(args):
             "cpu_baseline": cpu_baseline,
             "sections": extra,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), file=args.out)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def _own_stdout():
+    """Returns a file object on the real stdout and points fd 1 at stderr for the rest of the run, so
+    that library banners (NCCL prints its version on stdout) cannot break the one-JSON-line contract."""
+    sys.stdout.flush()
+    real = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return real
 
 
 def main():
@@ -445,10 +454,12 @@ def main():
     ap.add_argument("--sections", choices=["all", "none"], default="all")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
+    args.out = _own_stdout()
     if args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
+    args.out.flush()
 
 
 if __name__ == "__main__":

@@ -86,6 +86,17 @@ int tb200_dequant_int8_rowwise(const void* w, const float* scale, void* out,
 int tb200_weight_dequant_block(const void* x, const void* s, void* y,
                                int64_t m, int64_t n, int64_t tile, int dtype, void* stream);
 
+/*
+ * FP8 e4m3 block quantiser — the step before tb200_gemm_fp8_blockscaled (the reference only has a cast,
+ * tilebench/benchmarks/operators/quantize_global/impl_torch.py:4-5).  One fp32 scale = amax / 448 per
+ * [block_rows x 128] block (1 for an all-zero block), q = e4m3(x / scale) rounded to nearest even.
+ *   x fp32 [rows, cols]   q e4m3 [rows, cols]   scales fp32 [rows / block_rows, cols / 128]
+ * block_rows is 1 (activations) or 128 (weights); cols a multiple of 128.  Bit-exact against the same
+ * formula in PyTorch.
+ */
+int tb200_quantize_fp8_block(const float* x, void* q, float* scales, int64_t rows, int64_t cols,
+                             int block_rows, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Quantised GEMMs on tcgen05 tensor cores (TMA operands, TMEM accumulators).
  * ------------------------------------------------------------------------------------------- */

@@ -195,3 +195,18 @@ def test_runs_under_cuda_graph_capture(cuda_device):
     g.replay()
     torch.cuda.synchronize()
     assert np.array_equal(bits16(out), ref_ops.dequant_int8_channel(w.cpu().numpy(), s.cpu().numpy()))
+
+
+@pytest.mark.parametrize("rows,cols,block_rows", [(256, 512, 1), (3, 128, 1), (256, 384, 128), (1024, 1024, 128)])
+def test_fp8_block_quantiser_bit_exact(cuda_device, rows, cols, block_rows):
+    """q and scales must equal the PyTorch formula bit for bit, including an all-zero block and +-amax."""
+    from tilebench_b200.benchmarks.operators.quantize_fp8_block import impl_cuda, impl_torch
+    x = torch.randn(rows, cols, generator=torch.Generator().manual_seed(rows + cols))
+    x[0, :128] = 0.0
+    if block_rows == 128:
+        x[:128, :128] = 0.0
+    q, s = impl_cuda.run(x.to(cuda_device), block_rows)
+    q_ref, s_ref = impl_torch.run(x, block_rows)
+    assert torch.equal(s.cpu(), s_ref)
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+    assert q.cpu().float().abs().max() == 448.0

@@ -90,14 +90,6 @@ tb200_k_dequant_int4_group(const uint32_t* wp, const __half* scales, __half* out
                            uint32_t gpr, uint64_t total, int64_t ldo, float zp1024) {
     dequant_int4_group_body<4>(wp, scales, out, cpr, gc, gpr, total, ldo, zp1024);
 }
-// Same kernel with eight chunks in flight per thread: used when that lets one wave of CTAs cover the
-// whole matrix in a single pass (mid-sized matrices, where a second pass would mostly be latency).
-extern "C" __global__ void __launch_bounds__(kThreads)
-tb200_k_dequant_int4_group_u8(const uint32_t* wp, const __half* scales, __half* out, uint32_t cpr, uint32_t gc,
-                              uint32_t gpr, uint64_t total, int64_t ldo, float zp1024) {
-    dequant_int4_group_body<8>(wp, scales, out, cpr, gc, gpr, total, ldo, zp1024);
-}
-
 // Any even k, any group that divides k: one output element per thread.
 extern "C" __global__ void __launch_bounds__(kThreads)
 tb200_k_dequant_int4_group_scalar(const uint8_t* __restrict__ wp, const __half* __restrict__ scales,
@@ -345,12 +337,8 @@ extern "C" int tb200_dequant_int4_group(const void* wp, const void* scales, void
                      ((reinterpret_cast<uintptr_t>(wp) & 3u) == 0) && (k / 8 < (1ll << 32));
     if (vec) {
         uint64_t total = static_cast<uint64_t>(n) * static_cast<uint64_t>(k / 8);
-        const uint64_t cap = static_cast<uint64_t>(num_sms()) * (2048 / kThreads);
-        const uint64_t need4 = (total + kThreads * 4 - 1) / (kThreads * 4), need8 = (total + kThreads * 8 - 1) / (kThreads * 8);
-        const bool one_pass_u8 = need4 > cap && need8 <= cap;
-        unsigned grid = grid_for(total, kThreads, one_pass_u8 ? 8 : 4);
-        auto kern = one_pass_u8 ? tb200_k_dequant_int4_group_u8 : tb200_k_dequant_int4_group;
-        kern<<<grid, kThreads, 0, st>>>(
+        unsigned grid = grid_for(total, kThreads, kUnroll);
+        tb200_k_dequant_int4_group<<<grid, kThreads, 0, st>>>(
             static_cast<const uint32_t*>(wp), static_cast<const __half*>(scales), static_cast<__half*>(out),
             static_cast<uint32_t>(k / 8), static_cast<uint32_t>(group / 8), static_cast<uint32_t>(k / group), total,
             ldo, 1024.0f + static_cast<float>(zero_point));

@@ -150,6 +150,18 @@ void gemm_w4a16_gather(const torch::Tensor& a, const torch::Tensor& wp, const to
              "tb200_gemm_w4a16_gather");
 }
 
+void quantize_fp8_block(const torch::Tensor& x, torch::Tensor& q, torch::Tensor& scales, int64_t block_rows) {
+    check_cuda(x, "x", torch::kFloat32);
+    check_cuda(q, "q", torch::kFloat8_e4m3fn);
+    check_cuda(scales, "scales", torch::kFloat32);
+    TORCH_CHECK(x.dim() == 2 && q.sizes() == x.sizes(), "x and q must be [rows, cols]");
+    TORCH_CHECK(block_rows > 0 && scales.numel() == (x.size(0) / block_rows) * (x.size(1) / 128), "scales must be [rows/block_rows, cols/128]");
+    c10::cuda::CUDAGuard guard(x.device());
+    check_rc(tb200_quantize_fp8_block(x.data_ptr<float>(), q.data_ptr(), scales.data_ptr<float>(), x.size(0), x.size(1),
+                                      static_cast<int>(block_rows), stream_of(x)),
+             "tb200_quantize_fp8_block");
+}
+
 py::tuple device_status() {
     int code = 0, detail = 0;
     check_rc(tb200_device_status(&code, &detail), "tb200_device_status");
@@ -172,6 +184,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_w4a16_workspace_bytes", &gemm_w4a16_workspace_bytes);
     m.def("gemm_w4a16", &gemm_w4a16);
     m.def("gemm_w4a16_gather", &gemm_w4a16_gather);
+    m.def("quantize_fp8_block", &quantize_fp8_block);
     m.def("device_status", &device_status);
     m.def("clear_device_status", &clear_device_status);
 }

@@ -96,7 +96,9 @@ def quantize_fp8_blockwise(x: torch.Tensor, block_rows: int, block_cols: int = 1
     R, C = x.shape
     xb = x.reshape(R // block_rows, block_rows, C // block_cols, block_cols)
     amax = xb.abs().amax(dim=(1, 3))
-    scale = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax)).to(torch.float32)
+    # tensor / tensor: a true IEEE division on every device (tensor / python-scalar becomes a multiplication
+    # by the rounded reciprocal on CUDA, which differs from amax / 448 in the last bit for most blocks)
+    scale = torch.where(amax > 0, amax / torch.full_like(amax, FP8_MAX), torch.ones_like(amax)).to(torch.float32)
     q = (xb / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).reshape(R, C).to(torch.float8_e4m3fn)
     return q, scale
 
@@ -118,6 +120,12 @@ def generate_gemm_w4a16_npart_inputs(M, K, N, WORLD=1, GATHER=1, GROUP=128, ZP=8
                                      device=DEFAULT_DEVICE, seed=SEED0 + 4000, **kwargs):
     a, wp, scales, group, zp = generate_gemm_w4a16_inputs(M, K, N, GROUP, ZP, device=device, seed=seed)
     return (a, wp, scales, group, zp, WORLD, GATHER)
+
+
+def generate_quantize_fp8_block_inputs(S, BLOCK_ROWS=1, dtype=torch.float32, device=DEFAULT_DEVICE,
+                                       seed=SEED0 + 7000, **kwargs):
+    x = torch.randn(S, S, generator=_gen(seed))
+    return (x.to(device), int(BLOCK_ROWS))
 
 
 # ---- the reference's own operators (seeded versions of tensors.py:179-184 and :492-499) -------
@@ -144,6 +152,7 @@ GENERATORS = {
     "gemm_w4a16": generate_gemm_w4a16_inputs,
     "gemm_fp8_blockscaled": generate_gemm_fp8_blockscaled_inputs,
     "gemm_w4a16_npart": generate_gemm_w4a16_npart_inputs,
+    "quantize_fp8_block": generate_quantize_fp8_block_inputs,
     "dequantize_rowwise": generate_dequantize_rowwise_inputs,
     "weight_dequant": generate_weight_dequant_inputs,
 }
@@ -169,6 +178,8 @@ def infer_problem_size(operator_name, params):
     if operator_name == "gemm_fp8_blockscaled":
         s = int(p.get("S") or 0)
         return int(p.get("M") or s) * int(p.get("N") or s)
+    if operator_name == "quantize_fp8_block":
+        return int(p["S"]) ** 2
     if operator_name == "weight_dequant":
         return int(p["M"]) * int(p.get("N") or p["M"])
     return 1
