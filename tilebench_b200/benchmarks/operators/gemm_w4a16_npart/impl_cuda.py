@@ -1,5 +1,6 @@
-"""cuda backend of gemm_w4a16_npart: each rank runs tb200_gemm_w4a16 on its slice of the weight
-rows; with GATHER the column slices are all-gathered over NCCL (tilebench_b200.npart)."""
+"""cuda backend of gemm_w4a16_npart: each rank runs the W4A16 GEMM on its slice of the weight rows.
+GATHER = 0 keeps the per-rank column slice, 1 all-gathers the slices with NCCL, 2 lets the GEMM epilogue
+store every tile into all ranks' output buffers (tilebench_b200.npart)."""
 import torch
 
 from tilebench_b200 import npart
@@ -10,7 +11,8 @@ def run(a, wp, scales, GROUP: int = 128, ZP: int = 8, WORLD: int = 1, GATHER: in
     if int(WORLD) != world:
         raise RuntimeError(f"gemm_w4a16_npart: case wants WORLD={WORLD} ranks, process group has {world}")
     lo, hi = npart.partition(wp.shape[0], world, rank)
-    out = npart.gemm_w4a16_partitioned(a, wp[lo:hi], scales[lo:hi], int(GROUP), int(ZP), gather=bool(GATHER))
+    mode = {0: False, 1: "nccl", 2: "fused"}[int(GATHER)]
+    out = npart.gemm_w4a16_partitioned(a, wp[lo:hi], scales[lo:hi], int(GROUP), int(ZP), gather=mode)
     if not GATHER and world > 1:
         # verification compares against the full product: place the local slice, leave the rest to the peers
         raise RuntimeError("gemm_w4a16_npart: GATHER=0 leaves a column slice per rank; verify it with npart tests")
