@@ -80,6 +80,23 @@ def test_fp8_4096_cube_vs_torch_reference(cuda_device):
     assert torch.equal(out, again)                      # run-to-run deterministic
 
 
+@pytest.mark.parametrize("variant", ["pair", "n256", "n128"])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 256), (300, 512, 1024), (1000, 1792, 512), (2048, 2048, 2048)])
+def test_fp8_kernel_variants_agree_bit_for_bit(cuda_device, monkeypatch, variant, M, N, K):
+    # The CTA-pair kernel (one MMA across two SMs), the 128 x 256 and the 128 x 128 kernel add the same
+    # scaled K-block products in the same order: their results must be identical, ragged M included.
+    from tilebench_b200.benchmarks.operators.gemm_fp8_blockscaled import impl_cuda
+    inputs = [t.to(cuda_device) for t in tensors.generate_gemm_fp8_blockscaled_inputs(M=M, N=N, K=K, device="cpu", seed=M + K)]
+    native.clear_device_status()
+    monkeypatch.delenv("TB200_FP8_VARIANT", raising=False)
+    base = impl_cuda.run(*inputs)
+    monkeypatch.setenv("TB200_FP8_VARIANT", variant)
+    other = impl_cuda.run(*inputs)
+    torch.cuda.synchronize()
+    status_clean()
+    assert torch.equal(base, other)
+
+
 def test_fp8_rejects_bad_shapes(cuda_device):
     ext = native.load()
     a = torch.zeros(128, 192, device=cuda_device).to(torch.float8_e4m3fn)
