@@ -114,6 +114,19 @@ int tb200_gemm_fp8_blockscaled(const void* a, const float* sa, const void* b, co
                                void* stream);
 
 /*
+ * int8 x packed-2-bit GEMM — the reference operator `matmul_int8`
+ * (tilebench/benchmarks/operators/matmul_int8/impl_torch.py:4-19; generator tilebench/data/tensors.py:439-448).
+ *   a    int8  [m, k]
+ *   b    uint8 [k/4, n]: bits [2i, 2i+2) of b[kb, j] hold weight B[i * k/4 + kb, j] + 1, i = 0..3
+ *   out  int32 [m, ldo]:  out[r, j] = sum_k a[r, k] * B[k, j],  B in {-1, 0, 1, 2}
+ * Integer arithmetic on the tensor cores (tcgen05 kind::i8, int32 accumulation): the result is exact
+ * whatever the summation order.  k a multiple of 256 and n of 128 (TB200_ERR_UNSUPPORTED otherwise),
+ * ldo >= n and a multiple of 4; a, b, out 16-byte aligned.
+ */
+int tb200_matmul_int8_packed2(const void* a, const void* b, void* out, int64_t m, int64_t n, int64_t k,
+                              int64_t ldo, void* stream);
+
+/*
  * W4A16 dequant-fused GEMM (new operator `gemm_w4a16`; structural template: the packed-weight
  * GEMM tilebench/benchmarks/operators/matmul_int8/impl_torch.py:4-19).
  *   a       fp16  [m, k]

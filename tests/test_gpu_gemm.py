@@ -198,3 +198,72 @@ def test_w4a16_workspace_too_small_is_an_error(cuda_device):
     out = torch.empty(24, 14336, dtype=torch.float16, device=cuda_device)
     with pytest.raises(ValueError):
         ext.gemm_w4a16(a, wp, sc, out, group, zp, 0, None)
+
+
+# ---------------------------------------------------------------- int8 x packed 2-bit (reference operator matmul_int8)
+
+def i8_run(a, b, device):
+    from tilebench_b200.benchmarks.operators.matmul_int8 import impl_cuda
+    native.clear_device_status()
+    out = impl_cuda.run(a.to(device), b.to(device))
+    torch.cuda.synchronize()
+    status_clean()
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("N", [128, 256, 512, 4864])      # 4864: enough 256-wide tiles for the wide kernel
+def test_int8_one_hot_rows_read_out_every_unpacked_weight(cuda_device, N):
+    # a = one-hot rows: out[r, :] is row k_r of the unpacked weight matrix, so every (k, n) position of the
+    # operand layout (field plane, swizzle, 128-column block, sub-step) is pinned individually.
+    K = 512
+    g = torch.Generator().manual_seed(N)
+    b = torch.randint(0, 256, (K // 4, N), dtype=torch.uint8, generator=g)
+    a = torch.zeros(K, K, dtype=torch.int8)
+    a[torch.arange(K), torch.arange(K)] = 1
+    got = i8_run(a, b, cuda_device)
+    want = ref_ops.matmul_int8_packed2bit(a.numpy(), b.numpy())
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 256), (100, 256, 512), (128, 384, 1024), (300, 2048, 2048), (2048, 2048, 1024)])
+def test_int8_matches_oracle_exactly(cuda_device, M, N, K):
+    a, b = tensors.generate_matmul_int8_inputs(M, N, K, device="cpu", seed=M + N + K)
+    got = i8_run(a, b, cuda_device)
+    assert np.array_equal(got, ref_ops.matmul_int8_packed2bit(a.numpy(), b.numpy()))
+
+
+def test_int8_extreme_values_and_longest_k(cuda_device):
+    # a = -128 / 127 everywhere with weights 2 / -1: the largest magnitudes the format allows, K = 20480
+    from tilebench_b200.benchmarks.operators.matmul_int8 import impl_torch
+    M, N, K = 256, 256, 20480
+    a = torch.full((M, K), 127, dtype=torch.int8)
+    a[::2] = -128
+    b = torch.full((K // 4, N), 0xFF, dtype=torch.uint8)      # every field 3 -> weight 2
+    b[:, ::2] = 0x00                                          # every field 0 -> weight -1
+    got = i8_run(a, b, cuda_device)
+    want = np.empty((M, N), dtype=np.int64)
+    want[0::2, 0::2] = -128 * -1 * K
+    want[0::2, 1::2] = -128 * 2 * K
+    want[1::2, 0::2] = 127 * -1 * K
+    want[1::2, 1::2] = 127 * 2 * K
+    assert np.array_equal(got.astype(np.int64), want)
+    a2, b2 = tensors.generate_matmul_int8_inputs(2048, 2048, K, device=cuda_device, seed=3)
+    out = impl_cuda_i8(a2, b2)
+    assert torch.equal(out, impl_torch.run(a2, b2))
+
+
+def impl_cuda_i8(a, b):
+    from tilebench_b200.benchmarks.operators.matmul_int8 import impl_cuda
+    native.clear_device_status()
+    out = impl_cuda.run(a, b)
+    torch.cuda.synchronize()
+    status_clean()
+    return out
+
+
+def test_int8_rejects_unsupported_shapes(cuda_device):
+    ext = native.load()
+    a = torch.zeros(16, 200, dtype=torch.int8, device=cuda_device)
+    b = torch.zeros(50, 128, dtype=torch.uint8, device=cuda_device)
+    with pytest.raises(Exception):
+        ext.matmul_int8_packed2(a, b, torch.empty(16, 128, dtype=torch.int32, device=cuda_device))

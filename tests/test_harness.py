@@ -28,7 +28,7 @@ def test_backend_registry():
 
 def test_case_counts_match_the_configs():
     want = {"dequant_int4_group": 1, "dequant_int8_channel": 3, "gemm_w4a16": 4, "gemm_fp8_blockscaled": 4,
-            "gemm_w4a16_npart": 12, "dequantize_rowwise": 20, "weight_dequant": 60, "quantize_fp8_block": 6}
+            "gemm_w4a16_npart": 12, "dequantize_rowwise": 20, "weight_dequant": 60, "quantize_fp8_block": 6, "matmul_int8": 20}
     assert sorted(list_operators()) == sorted(want)
     for op, n in want.items():
         cfg = yaml.safe_load(open(operator_config(op)))
@@ -59,6 +59,11 @@ def test_generators_are_seeded_and_shaped():
     aq, sa, bq, sb = tensors.generate_gemm_fp8_blockscaled_inputs(S=256, device="cpu")
     assert aq.dtype == torch.float8_e4m3fn and sa.shape == (256, 2) and sb.shape == (2, 2)
     assert tensors.infer_problem_size("gemm_w4a16", {"M": 16, "N": 14336, "K": 4096}) == 16 * 14336
+    a8, b8 = tensors.generate_matmul_int8_inputs(8, 16, 64, device="cpu")
+    assert a8.dtype == torch.int8 and a8.shape == (8, 64) and int(a8.min()) >= -64 and int(a8.max()) <= 64
+    assert b8.dtype == torch.uint8 and b8.shape == (16, 16)
+    with pytest.raises(ValueError):
+        tensors.generate_matmul_int8_inputs(8, 16, 66, device="cpu")
 
 
 def test_dtypes():

@@ -162,6 +162,18 @@ void quantize_fp8_block(const torch::Tensor& x, torch::Tensor& q, torch::Tensor&
              "tb200_quantize_fp8_block");
 }
 
+void matmul_int8_packed2(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& out) {
+    check_cuda(a, "a", torch::kInt8);
+    check_cuda(b, "b", torch::kUInt8);
+    check_cuda(out, "out", torch::kInt32);
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == 4 * b.size(0), "a [m,k], b [k/4,n]");
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == a.size(0) && out.size(1) == b.size(1) && out.stride(1) == 1, "out must be [m,n]");
+    c10::cuda::CUDAGuard guard(a.device());
+    check_rc(tb200_matmul_int8_packed2(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.size(0), b.size(1), a.size(1),
+                                       out.stride(0), stream_of(a)),
+             "tb200_matmul_int8_packed2");
+}
+
 py::tuple device_status() {
     int code = 0, detail = 0;
     check_rc(tb200_device_status(&code, &detail), "tb200_device_status");
@@ -185,6 +197,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_w4a16", &gemm_w4a16);
     m.def("gemm_w4a16_gather", &gemm_w4a16_gather);
     m.def("quantize_fp8_block", &quantize_fp8_block);
+    m.def("matmul_int8_packed2", &matmul_int8_packed2);
     m.def("device_status", &device_status);
     m.def("clear_device_status", &clear_device_status);
 }

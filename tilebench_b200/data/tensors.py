@@ -146,6 +146,17 @@ def generate_weight_dequant_inputs(M, TILE_SIZE, dtype, N=None, device=DEFAULT_D
     return (X.to(device), S.to(device), M, N, TILE_SIZE)
 
 
+def generate_matmul_int8_inputs(M, N, K, device=DEFAULT_DEVICE, seed=SEED0 + 7000, **kwargs):
+    """Seeded version of tilebench/data/tensors.py:439-448: a int8 in [-64, 64], b uint8 [K/4, N] with four
+    2-bit fields per byte (all 256 byte values, so every field takes every value 0..3)."""
+    if K % 4:
+        raise ValueError("K must be divisible by 4 (b holds four fields per byte)")
+    g = _gen(seed)
+    a = torch.randint(-64, 65, (M, K), dtype=torch.int8, generator=g)
+    b = torch.randint(0, 256, (K // 4, N), dtype=torch.uint8, generator=g)
+    return (a.to(device), b.to(device))
+
+
 GENERATORS = {
     "dequant_int4_group": generate_dequant_int4_group_inputs,
     "dequant_int8_channel": generate_dequant_int8_channel_inputs,
@@ -155,6 +166,7 @@ GENERATORS = {
     "quantize_fp8_block": generate_quantize_fp8_block_inputs,
     "dequantize_rowwise": generate_dequantize_rowwise_inputs,
     "weight_dequant": generate_weight_dequant_inputs,
+    "matmul_int8": generate_matmul_int8_inputs,
 }
 
 
@@ -182,4 +194,6 @@ def infer_problem_size(operator_name, params):
         return int(p["S"]) ** 2
     if operator_name == "weight_dequant":
         return int(p["M"]) * int(p.get("N") or p["M"])
+    if operator_name == "matmul_int8":
+        return 2 * int(p["M"]) * int(p["N"]) * int(p["K"])       # the reference sizes GEMMs by FLOPs (tensors.py:703-704)
     return 1
