@@ -267,3 +267,92 @@ def test_int8_rejects_unsupported_shapes(cuda_device):
     b = torch.zeros(50, 128, dtype=torch.uint8, device=cuda_device)
     with pytest.raises(Exception):
         ext.matmul_int8_packed2(a, b, torch.empty(16, 128, dtype=torch.int32, device=cuda_device))
+
+
+# ---------------------------------------------------------------- plain GEMM (reference operator matmul_fp32_fp16_fp8)
+
+def plain_run(a, b):
+    from tilebench_b200.benchmarks.operators.matmul_fp32_fp16_fp8 import impl_cuda
+    native.clear_device_status()
+    out = impl_cuda.run(a, b)
+    torch.cuda.synchronize()
+    status_clean()
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.float8_e4m3fn])
+@pytest.mark.parametrize("N", [128, 256, 4864])          # 4864: enough 256-wide tiles for the wide kernel
+def test_plain_one_hot_rows_read_out_b_exactly(cuda_device, dtype, N):
+    # a = identity: out must equal b bit for bit (every value of b is exact in tf32 / fp16 / e4m3), which pins
+    # the MN-major operand layout of b — column block, swizzle, K step — element by element.
+    K = 512
+    g = torch.Generator().manual_seed(N)
+    b = torch.randint(-8, 9, (K, N), generator=g).to(torch.float32).to(dtype).to(cuda_device)
+    a = torch.eye(K, dtype=torch.float32).to(dtype).to(cuda_device)
+    out = plain_run(a, b)
+    assert torch.equal(out.view(torch.uint8), b.view(torch.uint8))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 128), (100, 256, 512), (300, 384, 1024), (2048, 2048, 1024)])
+def test_plain_fp16_matches_oracle(cuda_device, M, N, K):
+    a, b = tensors.generate_matmul_fp32_fp16_fp8_inputs(M, N, K, dtype=torch.float16, device="cpu", seed=M + N + K)
+    got = plain_run(a.to(cuda_device), b.to(cuda_device)).cpu().numpy().astype(np.float32)
+    want = ref_ops.matmul_plain(a.numpy(), b.numpy(), "fp16").astype(np.float32)
+    np.testing.assert_allclose(got, want, atol=1e-3, rtol=1e-3)       # fp16 tolerance of the reference's verifier
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 32), (100, 256, 512), (300, 384, 1024), (2048, 2048, 1024)])
+def test_plain_fp32_is_a_tf32_gemm(cuda_device, M, N, K):
+    a, b = tensors.generate_matmul_fp32_fp16_fp8_inputs(M, N, K, dtype=torch.float32, device="cpu", seed=M + N + K)
+    got = plain_run(a.to(cuda_device), b.to(cuda_device)).cpu().numpy()
+    want = ref_ops.matmul_plain(a.numpy(), b.numpy(), "tf32")         # operands with the low 13 mantissa bits dropped
+    np.testing.assert_allclose(got, want, atol=1e-4, rtol=1e-4)
+    # and within TF32's input precision (2**-10 relative per operand) of the true fp32 product
+    np.testing.assert_allclose(got, ref_ops.matmul_plain(a.numpy(), b.numpy(), "fp32"), atol=5e-3, rtol=5e-3)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 128), (100, 256, 512), (300, 384, 1024), (2048, 2048, 2048)])
+def test_plain_fp8_matches_oracle_up_to_rounding_ties(cuda_device, M, N, K):
+    a, b = tensors.generate_matmul_fp32_fp16_fp8_inputs(M, N, K, dtype=torch.float8_e4m3fn, device="cpu", seed=M + N + K)
+    got = plain_run(a.to(cuda_device), b.to(cuda_device)).cpu().view(torch.uint8).numpy()
+    want = ref_ops.matmul_plain(a.view(torch.uint8).numpy(), b.view(torch.uint8).numpy(), "fp8")
+    # Products of e4m3 values are exact in fp32; only the order of the fp32 additions differs, which can move
+    # a sum across a bf16 / e4m3 rounding boundary: such elements differ by one e4m3 step and are rare.
+    diff = got != want
+    assert diff.mean() < 2e-3
+    step = np.abs(got[diff].astype(np.int16) - want[diff].astype(np.int16))
+    assert step.size == 0 or step.max() == 1
+
+
+def test_plain_fp8_overflow_becomes_nan_like_torch(cuda_device):
+    # 28 * 16 = 448 (largest finite), 30 * 16 = 480 and -30 * 16 overflow: PyTorch's cast gives NaN, not 448
+    K, N = 128, 128
+    a = torch.zeros(4, K)
+    a[0, 0], a[1, 0], a[2, 0], a[3, 0] = 28.0, 30.0, -30.0, 1.0
+    b = torch.zeros(K, N)
+    b[0, :] = 16.0
+    out = plain_run(a.to(torch.float8_e4m3fn).to(cuda_device), b.to(torch.float8_e4m3fn).to(cuda_device)).float().cpu()
+    assert torch.all(out[0] == 448.0) and torch.all(out[3] == 16.0)
+    assert torch.isnan(out[1]).all() and torch.isnan(out[2]).all()
+
+
+@pytest.mark.parametrize("dtype,K", [(torch.float16, 4096), (torch.float32, 2048), (torch.float8_e4m3fn, 8192)])
+def test_plain_reference_shape_vs_torch_reference(cuda_device, dtype, K):
+    from tilebench_b200.benchmarks.operators.matmul_fp32_fp16_fp8 import impl_torch
+    from tilebench_b200.core import verifier
+    a, b = tensors.generate_matmul_fp32_fp16_fp8_inputs(4096, 4096, K, dtype=dtype, device=cuda_device, seed=K)
+    out = plain_run(a, b)
+    ok, err = verifier.verify(out, impl_torch.run(a, b), atol=5.0, rtol=0.1)     # the reference's own tolerance
+    assert ok, err
+    tight = {torch.float16: 2e-3, torch.float32: 5e-3, torch.float8_e4m3fn: 0.13}[dtype]
+    torch.testing.assert_close(out.float(), impl_torch.run(a, b).float(), atol=tight, rtol=tight)
+    assert torch.equal(out.view(torch.uint8), plain_run(a, b).view(torch.uint8))    # deterministic
+
+
+def test_plain_rejects_unsupported(cuda_device):
+    from tilebench_b200.benchmarks.operators.matmul_fp32_fp16_fp8 import impl_cuda
+    a = torch.zeros(16, 100, dtype=torch.float16, device=cuda_device)
+    with pytest.raises(Exception):
+        impl_cuda.run(a, torch.zeros(100, 128, dtype=torch.float16, device=cuda_device))
+    with pytest.raises(NotImplementedError):
+        impl_cuda.run(a.to(torch.bfloat16), torch.zeros(100, 128, dtype=torch.bfloat16, device=cuda_device))

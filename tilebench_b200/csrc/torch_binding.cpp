@@ -174,6 +174,23 @@ void matmul_int8_packed2(const torch::Tensor& a, const torch::Tensor& b, torch::
              "tb200_matmul_int8_packed2");
 }
 
+void matmul_plain(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& out) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "matmul_plain: tensors must be on a CUDA device");
+    TORCH_CHECK(a.is_contiguous() && b.is_contiguous(), "matmul_plain: a and b must be contiguous");
+    TORCH_CHECK(a.scalar_type() == b.scalar_type() && a.scalar_type() == out.scalar_type(), "matmul_plain: a, b, out must share a dtype");
+    int dt = -1;
+    if (a.scalar_type() == torch::kFloat32) dt = TB200_DT_F32;
+    else if (a.scalar_type() == torch::kFloat16) dt = TB200_DT_F16;
+    else if (a.scalar_type() == torch::kFloat8_e4m3fn) dt = TB200_DT_F8E4M3;
+    if (dt < 0) throw py::type_error("matmul_plain: dtype must be float32, float16 or float8_e4m3fn");
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(0), "a [m,k], b [k,n]");
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == a.size(0) && out.size(1) == b.size(1) && out.stride(1) == 1, "out must be [m,n]");
+    c10::cuda::CUDAGuard guard(a.device());
+    check_rc(tb200_matmul_plain(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.size(0), b.size(1), a.size(1), dt,
+                                out.stride(0), stream_of(a)),
+             "tb200_matmul_plain");
+}
+
 py::tuple device_status() {
     int code = 0, detail = 0;
     check_rc(tb200_device_status(&code, &detail), "tb200_device_status");
@@ -198,6 +215,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_w4a16_gather", &gemm_w4a16_gather);
     m.def("quantize_fp8_block", &quantize_fp8_block);
     m.def("matmul_int8_packed2", &matmul_int8_packed2);
+    m.def("matmul_plain", &matmul_plain);
     m.def("device_status", &device_status);
     m.def("clear_device_status", &clear_device_status);
 }

@@ -157,6 +157,16 @@ def generate_matmul_int8_inputs(M, N, K, device=DEFAULT_DEVICE, seed=SEED0 + 700
     return (a.to(device), b.to(device))
 
 
+def generate_matmul_fp32_fp16_fp8_inputs(M, N, K, dtype=torch.float32, device=DEFAULT_DEVICE, seed=SEED0 + 8000, **kwargs):
+    """Seeded version of tilebench/data/tensors.py:416-436: standard normal operands scaled by K**-0.5 so
+    the output stays O(1) whatever K is; fp8 operands are made in fp32 and cast."""
+    g = _gen(seed)
+    scale = K ** -0.5
+    a = (torch.randn(M, K, dtype=torch.float32, generator=g) * scale).to(dtype)
+    b = (torch.randn(K, N, dtype=torch.float32, generator=g) * scale).to(dtype)
+    return (a.to(device), b.to(device))
+
+
 GENERATORS = {
     "dequant_int4_group": generate_dequant_int4_group_inputs,
     "dequant_int8_channel": generate_dequant_int8_channel_inputs,
@@ -167,6 +177,7 @@ GENERATORS = {
     "dequantize_rowwise": generate_dequantize_rowwise_inputs,
     "weight_dequant": generate_weight_dequant_inputs,
     "matmul_int8": generate_matmul_int8_inputs,
+    "matmul_fp32_fp16_fp8": generate_matmul_fp32_fp16_fp8_inputs,
 }
 
 
@@ -194,6 +205,6 @@ def infer_problem_size(operator_name, params):
         return int(p["S"]) ** 2
     if operator_name == "weight_dequant":
         return int(p["M"]) * int(p.get("N") or p["M"])
-    if operator_name == "matmul_int8":
+    if operator_name in ("matmul_int8", "matmul_fp32_fp16_fp8"):
         return 2 * int(p["M"]) * int(p["N"]) * int(p["K"])       # the reference sizes GEMMs by FLOPs (tensors.py:703-704)
     return 1
