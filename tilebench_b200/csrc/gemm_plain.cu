@@ -125,6 +125,16 @@ __device__ __forceinline__ void pl_store32(float* dst, const uint32_t (&v)[32]) 
     for (int q = 0; q < 8; ++q)
         *reinterpret_cast<uint4*>(dst + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
 }
+// fp32 -> bf16 -> e4m3, both round-to-nearest-even.  The hardware conversion saturates; PyTorch's cast does
+// not: a bf16 value above 464 (the last one that rounds down to 448) becomes NaN there, so it does here.
+__device__ __forceinline__ uint32_t pl_e4m3x2(float x, float y) {
+    const float rx = __bfloat162float(__float2bfloat16_rn(x));
+    const float ry = __bfloat162float(__float2bfloat16_rn(y));
+    uint32_t q = __nv_cvt_float2_to_fp8x2(make_float2(rx, ry), __NV_SATFINITE, __NV_E4M3);
+    if (fabsf(rx) > 464.0f) q |= 0x007Fu;
+    if (fabsf(ry) > 464.0f) q |= 0x7F00u;
+    return q;
+}
 __device__ __forceinline__ void pl_store32(uint8_t* dst, const uint32_t (&v)[32]) {
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
@@ -132,14 +142,9 @@ __device__ __forceinline__ void pl_store32(uint8_t* dst, const uint32_t (&v)[32]
         uint32_t* w = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            uint32_t word = 0;
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                // fp32 -> bf16 -> e4m3, both round-to-nearest-even; no saturation: overflow becomes NaN as in PyTorch's cast
-                const float r = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[16 * q + 4 * e + b])));
-                word |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(r, __NV_NOSAT, __NV_E4M3)) << (8 * b);
-            }
-            w[e] = word;
+            const int i = 16 * q + 4 * e;
+            w[e] = pl_e4m3x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])) |
+                   (pl_e4m3x2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])) << 16);
         }
         *reinterpret_cast<uint4*>(dst + 16 * q) = o;
     }
