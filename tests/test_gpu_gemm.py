@@ -349,6 +349,18 @@ def test_plain_reference_shape_vs_torch_reference(cuda_device, dtype, K):
     assert torch.equal(out.view(torch.uint8), plain_run(a, b).view(torch.uint8))    # deterministic
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.float8_e4m3fn])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 256), (300, 512, 1024), (1000, 1792, 512), (2048, 2048, 2048)])
+def test_plain_pair_and_single_cta_kernels_agree_bit_for_bit(cuda_device, monkeypatch, dtype, M, N, K):
+    # the CTA-pair kernel (one MMA across two SMs) adds the same products in the same order as the single-CTA one
+    a, b = tensors.generate_matmul_fp32_fp16_fp8_inputs(M, N, K, dtype=dtype, device=cuda_device, seed=M + K)
+    monkeypatch.setenv("TB200_PLAIN_VARIANT", "single")
+    single = plain_run(a, b)
+    monkeypatch.setenv("TB200_PLAIN_VARIANT", "pair")
+    pair = plain_run(a, b)
+    assert torch.equal(single.view(torch.uint8), pair.view(torch.uint8))
+
+
 def test_plain_rejects_unsupported(cuda_device):
     from tilebench_b200.benchmarks.operators.matmul_fp32_fp16_fp8 import impl_cuda
     a = torch.zeros(16, 100, dtype=torch.float16, device=cuda_device)
