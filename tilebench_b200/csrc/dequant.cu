@@ -36,6 +36,22 @@ __device__ __forceinline__ __half2 nib_pair_to_half2(uint32_t lo_src, uint32_t h
     return *reinterpret_cast<__half2*>(&h);
 }
 
+// 256-bit global accesses (sm_100): one instruction moves 32 bytes per thread, 1 KB per warp.  The
+// streaming kernels below are bound by HBM, and HBM efficiency on this part rises with the bytes each
+// thread has in flight and with stores that cover whole 32-byte sectors in one instruction.
+__device__ __forceinline__ void ldg256(const void* p, uint32_t (&r)[8]) {
+    asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "l"(p));
+}
+__device__ __forceinline__ void stg256(void* p, const uint32_t (&r)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]),
+                 "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+constexpr int kWideUnroll = 8;     // 256-bit loads in flight per thread
+constexpr int kWideUnroll4 = 4;    // the int4 kernel writes 4x what it reads: fewer chunks, same output in flight
+
 }  // namespace
 }  // namespace tb200
 
@@ -89,6 +105,61 @@ extern "C" __global__ void __launch_bounds__(kThreads)
 tb200_k_dequant_int4_group(const uint32_t* wp, const __half* scales, __half* out, uint32_t cpr, uint32_t gc,
                            uint32_t gpr, uint64_t total, int64_t ldo, float zp1024) {
     dequant_int4_group_body<4>(wp, scales, out, cpr, gc, gpr, total, ldo, zp1024);
+}
+
+// Wide variant: one thread-chunk = 16 packed bytes (one 128-bit load) = 32 outputs written by two
+// 256-bit stores.  Needs k % 32 == 0, group % 32 == 0 and 32-byte aligned output rows.
+extern "C" __global__ void __launch_bounds__(kThreads)
+tb200_k_dequant_int4_group_wide(const uint4* __restrict__ wp, const __half* __restrict__ scales, __half* __restrict__ out,
+                                uint32_t chunks_per_row, uint32_t group_chunks, uint32_t groups_per_row,
+                                uint64_t total_chunks, int64_t ldo, float zp_plus_1024) {
+    constexpr int U = kWideUnroll4;
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+    const __half2 bias = __float2half2_rn(zp_plus_1024);
+    for (uint64_t base = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; base < total_chunks;
+         base += stride * U) {
+        uint4 packed[U];
+        __half sc[U];
+        uint64_t off[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint64_t c = base + u * stride;
+            if (c < total_chunks) {
+                const uint64_t row = c / chunks_per_row;
+                const uint32_t cc = static_cast<uint32_t>(c - row * chunks_per_row);
+                packed[u] = __ldg(wp + c);
+                sc[u] = __ldg(scales + row * groups_per_row + cc / group_chunks);
+                off[u] = row * static_cast<uint64_t>(ldo) + static_cast<uint64_t>(cc) * 32;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint64_t c = base + u * stride;
+            if (c < total_chunks) {
+                const __half2 s2 = __half2half2(sc[u]);
+                const uint32_t words[4] = {packed[u].x, packed[u].y, packed[u].z, packed[u].w};
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t o[8];
+#pragma unroll
+                    for (int w = 0; w < 2; ++w) {
+                        const uint32_t lo = words[2 * h + w], hi = lo >> 4;
+                        __half2 v[4];
+                        v[0] = nib_pair_to_half2(lo, hi, 0x0400);
+                        v[1] = nib_pair_to_half2(lo, hi, 0x0501);
+                        v[2] = nib_pair_to_half2(lo, hi, 0x0602);
+                        v[3] = nib_pair_to_half2(lo, hi, 0x0703);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            v[i] = __hmul2(__hsub2(v[i], bias), s2);          // exact int, one rounding
+                            o[4 * w + i] = *reinterpret_cast<uint32_t*>(&v[i]);
+                        }
+                    }
+                    stg256(out + off[u] + 16 * h, o);
+                }
+            }
+        }
+    }
 }
 // Any even k, any group that divides k: one output element per thread.
 extern "C" __global__ void __launch_bounds__(kThreads)
@@ -190,6 +261,66 @@ tb200_k_dequant_int8_rowwise_f16_post(const uint2* w, const float* scale, uint4*
                                       uint64_t total, float post) {
     dequant_int8_rowwise_body<false, true>(w, scale, out, cpr, total, post);
 }
+
+// Wide variant: one thread-chunk = 32 int8 (one 256-bit load) = 64 output bytes (two 256-bit stores).
+// Needs cols % 32 == 0 and 32-byte aligned w and out.
+template <bool BF16, bool POST, int U>
+__device__ __forceinline__ void dequant_int8_rowwise_wide_body(const uint8_t* __restrict__ w, const float* __restrict__ scale,
+                                                               uint8_t* __restrict__ out, uint32_t chunks_per_row,
+                                                               uint64_t total_chunks, float post) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+    for (uint64_t base = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; base < total_chunks;
+         base += stride * U) {
+        uint32_t raw[U][8];
+        float sc[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint64_t c = base + u * stride;
+            if (c < total_chunks) {
+                ldg256(w + c * 32, raw[u]);
+                sc[u] = __ldg(scale + c / chunks_per_row);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint64_t c = base + u * stride;
+            if (c < total_chunks) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t o[8];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint32_t x = raw[u][4 * h + q] ^ 0x80808080u;
+                        float f[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            f[i] = __fmul_rn(s8_to_float(x, i), sc[u]);          // first fp32 rounding
+                            if (POST) f[i] = __fmul_rn(f[i], post);              // second fp32 rounding (reference order)
+                        }
+                        o[2 * q] = pack2<BF16>(f[0], f[1]);
+                        o[2 * q + 1] = pack2<BF16>(f[2], f[3]);
+                    }
+                    stg256(out + c * 64 + 32 * h, o);
+                }
+            }
+        }
+    }
+}
+// kWideUnroll chunks in flight per thread for large inputs; 2 for mid-sized ones, where the deep variant
+// would leave SMs without a CTA.
+#define TB200_INT8_WIDE(name, BF16, POST, U)                                                                        \
+    extern "C" __global__ void __launch_bounds__(kThreads)                                                         \
+    name(const uint8_t* w, const float* scale, uint8_t* out, uint32_t cpr, uint64_t total, float post) {           \
+        dequant_int8_rowwise_wide_body<BF16, POST, U>(w, scale, out, cpr, total, post);                            \
+    }
+TB200_INT8_WIDE(tb200_k_dequant_int8_rowwise_bf16_wide, true, false, kWideUnroll)
+TB200_INT8_WIDE(tb200_k_dequant_int8_rowwise_f16_wide, false, false, kWideUnroll)
+TB200_INT8_WIDE(tb200_k_dequant_int8_rowwise_bf16_post_wide, true, true, kWideUnroll)
+TB200_INT8_WIDE(tb200_k_dequant_int8_rowwise_f16_post_wide, false, true, kWideUnroll)
+TB200_INT8_WIDE(tb200_k_dequant_int8_rowwise_bf16_wide2, true, false, 2)
+TB200_INT8_WIDE(tb200_k_dequant_int8_rowwise_f16_wide2, false, false, 2)
+TB200_INT8_WIDE(tb200_k_dequant_int8_rowwise_bf16_post_wide2, true, true, 2)
+TB200_INT8_WIDE(tb200_k_dequant_int8_rowwise_f16_post_wide2, false, true, 2)
 
 // Any cols: one element per thread.
 extern "C" __global__ void __launch_bounds__(kThreads)
@@ -335,7 +466,16 @@ extern "C" int tb200_dequant_int4_group(const void* wp, const void* scales, void
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool vec = (group % 8 == 0) && (ldo % 8 == 0) && aligned16(out) &&
                      ((reinterpret_cast<uintptr_t>(wp) & 3u) == 0) && (k / 8 < (1ll << 32));
-    if (vec) {
+    const bool wide = (group % 32 == 0) && (ldo % 16 == 0) && ((reinterpret_cast<uintptr_t>(out) & 31u) == 0) &&
+                      aligned16(wp) && (k / 32 < (1ll << 32));
+    if (wide) {
+        const uint64_t total = static_cast<uint64_t>(n) * static_cast<uint64_t>(k / 32);
+        const unsigned grid = grid_for(total, kThreads, kWideUnroll4);
+        tb200_k_dequant_int4_group_wide<<<grid, kThreads, 0, st>>>(
+            static_cast<const uint4*>(wp), static_cast<const __half*>(scales), static_cast<__half*>(out),
+            static_cast<uint32_t>(k / 32), static_cast<uint32_t>(group / 32), static_cast<uint32_t>(k / group), total,
+            ldo, 1024.0f + static_cast<float>(zero_point));
+    } else if (vec) {
         uint64_t total = static_cast<uint64_t>(n) * static_cast<uint64_t>(k / 8);
         unsigned grid = grid_for(total, kThreads, kUnroll);
         tb200_k_dequant_int4_group<<<grid, kThreads, 0, st>>>(
@@ -364,7 +504,21 @@ extern "C" int tb200_dequant_int8_rowwise(const void* w, const float* scale, voi
     const bool bf16 = out_dtype == TB200_DT_BF16;
     const bool vec = (cols % 8 == 0) && aligned16(out) && ((reinterpret_cast<uintptr_t>(w) & 7u) == 0) &&
                      (cols / 8 < (1ll << 32));
-    if (vec) {
+    const bool wide = (cols % 32 == 0) && ((reinterpret_cast<uintptr_t>(out) & 31u) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(w) & 31u) == 0) && (cols / 32 < (1ll << 32));
+    const uint64_t wide_total = static_cast<uint64_t>(rows) * static_cast<uint64_t>(cols / 32);
+    const uint64_t sms = static_cast<uint64_t>(num_sms());
+    if (wide && wide_total >= sms * kThreads * 2) {
+        // deep variant once it still gives every SM two CTAs, else two chunks per thread
+        const bool deep = wide_total >= 2 * sms * kThreads * kWideUnroll;
+        const unsigned grid = grid_for(wide_total, kThreads, deep ? kWideUnroll : 2);
+        auto kern = deep ? (bf16 ? (use_post ? tb200_k_dequant_int8_rowwise_bf16_post_wide : tb200_k_dequant_int8_rowwise_bf16_wide)
+                                 : (use_post ? tb200_k_dequant_int8_rowwise_f16_post_wide : tb200_k_dequant_int8_rowwise_f16_wide))
+                         : (bf16 ? (use_post ? tb200_k_dequant_int8_rowwise_bf16_post_wide2 : tb200_k_dequant_int8_rowwise_bf16_wide2)
+                                 : (use_post ? tb200_k_dequant_int8_rowwise_f16_post_wide2 : tb200_k_dequant_int8_rowwise_f16_wide2));
+        kern<<<grid, kThreads, 0, st>>>(static_cast<const uint8_t*>(w), scale, static_cast<uint8_t*>(out),
+                                        static_cast<uint32_t>(cols / 32), wide_total, post);
+    } else if (vec) {
         uint64_t total = static_cast<uint64_t>(rows) * static_cast<uint64_t>(cols / 8);
         unsigned grid = grid_for(total, kThreads, kUnroll);
         auto kern = bf16 ? (use_post ? tb200_k_dequant_int8_rowwise_bf16_post : tb200_k_dequant_int8_rowwise_bf16)
