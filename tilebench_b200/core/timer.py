@@ -4,10 +4,12 @@ Protocol of the reference timer (tilebench/core/timer.py:208-284): `warmup` unti
 `repeat` timed calls, each preceded — outside the timed region — by a write of 2x the L2 size so
 the call starts cold; with `use_cuda_graph` the call is captured once and the replay is timed
 (capture failure falls back to eager, as in timer.py:129-143).  The reference sums kernel
-durations with the Proton profiler; here the timed quantity is a CUDA-event pair around each call
-on the launching stream, which adds the launch gap of the first kernel (a few microseconds) to
-very short operators.  `report_benchmark_batched` amortises that gap for roofline numbers by
-timing back-to-back calls on rotating buffers whose combined footprint exceeds L2.
+durations with the Proton profiler.  Here the timed quantity is a CUDA-event pair on the launching
+stream: in graph mode the two events are event-record NODES of the captured graph, directly before
+and after the operator's kernels, so the host-side launch gap stays outside the measurement; in
+eager mode the pair brackets the Python call and very short operators carry a few microseconds of
+launch gap.  `report_benchmark_batched` amortises that gap for roofline numbers by timing
+back-to-back calls on rotating buffers whose combined footprint exceeds L2.
 """
 from __future__ import annotations
 
@@ -50,9 +52,11 @@ def flush_l2_cache() -> None:
 
 
 def _prepare_runner(f: Callable, args: Sequence, kwargs: dict, use_cuda_graph: bool):
-    """Returns (runner, mode).  Graph mode: 3 eager calls on a side stream, then capture."""
+    """Returns (runner, mode, events).  Graph mode: 3 eager calls on a side stream, then capture with an
+    event-record node on either side of the call; `events` is that pair, or None when the events have to
+    be recorded around the runner by the caller."""
     if not use_cuda_graph:
-        return (lambda: f(*args, **kwargs)), "eager"
+        return (lambda: f(*args, **kwargs)), "eager", None
     try:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -61,13 +65,27 @@ def _prepare_runner(f: Callable, args: Sequence, kwargs: dict, use_cuda_graph: b
                 f(*args, **kwargs)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        try:
+            ev0 = torch.cuda.Event(enable_timing=True, external=True)
+            ev1 = torch.cuda.Event(enable_timing=True, external=True)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                ev0.record()
+                f(*args, **kwargs)
+                ev1.record()
+            graph.replay()
+            torch.cuda.synchronize()
+            ev0.elapsed_time(ev1)                      # raises if the events did not become timing nodes
+            return graph.replay, "graph", (ev0, ev1)
+        except Exception:
+            torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             f(*args, **kwargs)
-        return graph.replay, "graph"
+        return graph.replay, "graph", None
     except Exception:
         torch.cuda.synchronize()
-        return (lambda: f(*args, **kwargs)), "eager"
+        return (lambda: f(*args, **kwargs)), "eager", None
 
 
 def report_benchmark(f: Callable, args: Sequence = (), kwargs: dict | None = None, *, warmup: int = DEFAULT_WARMUP,
@@ -81,11 +99,16 @@ def report_benchmark(f: Callable, args: Sequence = (), kwargs: dict | None = Non
             flush_l2_cache()
         f(*args, **kwargs)
     torch.cuda.synchronize()
-    runner, mode = _prepare_runner(f, args, kwargs, use_cuda_graph)
+    runner, mode, graph_events = _prepare_runner(f, args, kwargs, use_cuda_graph)
     samples = []
     for _ in range(max(1, repeat)):
         if do_flush:
             flush_l2_cache()
+        if graph_events is not None:
+            runner()
+            torch.cuda.current_stream().synchronize()
+            samples.append(graph_events[0].elapsed_time(graph_events[1]))
+            continue
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         runner()

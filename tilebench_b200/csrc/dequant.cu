@@ -408,7 +408,55 @@ __device__ __forceinline__ void weight_dequant_body(const uint4* __restrict__ x,
         }
     }
 }
+
+// Wide variant: one thread-chunk = 32 bytes in, 32 bytes out (256-bit load and store); the scale is
+// constant over a chunk because the tile width is a multiple of the chunk width.
+template <int DT, int U>
+__device__ __forceinline__ void weight_dequant_wide_body(const uint8_t* __restrict__ x, const void* __restrict__ s,
+                                                         uint8_t* __restrict__ y, uint32_t chunks_per_row,
+                                                         uint32_t tile_chunks, uint32_t tile_rows, uint32_t s_cols,
+                                                         uint64_t total_chunks) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+    for (uint64_t base = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; base < total_chunks;
+         base += stride * U) {
+        uint32_t raw[U][8];
+        float sc[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint64_t c = base + u * stride;
+            if (c < total_chunks) {
+                const uint64_t row = c / chunks_per_row;
+                const uint32_t cc = static_cast<uint32_t>(c - row * chunks_per_row);
+                ldg256(x + c * 32, raw[u]);
+                sc[u] = Vec16<DT>::load_scale(s, (row / tile_rows) * s_cols + cc / tile_chunks);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint64_t c = base + u * stride;
+            if (c < total_chunks) {
+                const uint4 lo = Vec16<DT>::mul(make_uint4(raw[u][0], raw[u][1], raw[u][2], raw[u][3]), sc[u]);
+                const uint4 hi = Vec16<DT>::mul(make_uint4(raw[u][4], raw[u][5], raw[u][6], raw[u][7]), sc[u]);
+                const uint32_t o[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                stg256(y + c * 32, o);
+            }
+        }
+    }
+}
 }  // namespace
+
+#define TB200_WDQ_WIDE(name, DT, U)                                                                                 \
+    extern "C" __global__ void __launch_bounds__(kThreads)                                                         \
+    name(const uint8_t* x, const void* s, uint8_t* y, uint32_t cpr, uint32_t tc, uint32_t tr, uint32_t sc,         \
+         uint64_t total) {                                                                                         \
+        weight_dequant_wide_body<DT, U>(x, s, y, cpr, tc, tr, sc, total);                                          \
+    }
+TB200_WDQ_WIDE(tb200_k_weight_dequant_f32_wide, TB200_DT_F32, kWideUnroll)
+TB200_WDQ_WIDE(tb200_k_weight_dequant_f16_wide, TB200_DT_F16, kWideUnroll)
+TB200_WDQ_WIDE(tb200_k_weight_dequant_bf16_wide, TB200_DT_BF16, kWideUnroll)
+TB200_WDQ_WIDE(tb200_k_weight_dequant_f32_wide2, TB200_DT_F32, 2)
+TB200_WDQ_WIDE(tb200_k_weight_dequant_f16_wide2, TB200_DT_F16, 2)
+TB200_WDQ_WIDE(tb200_k_weight_dequant_bf16_wide2, TB200_DT_BF16, 2)
 
 extern "C" __global__ void __launch_bounds__(kThreads)
 tb200_k_weight_dequant_f32(const uint4* x, const void* s, uint4* y, uint32_t cpr, uint32_t tc, uint32_t tr,
@@ -547,7 +595,22 @@ extern "C" int tb200_weight_dequant_block(const void* x, const void* s, void* y,
     const int elems = dtype == TB200_DT_F32 ? 4 : 8;
     const bool vec = (n % elems == 0) && (tile % elems == 0) && aligned16(x) && aligned16(y) &&
                      (n / elems < (1ll << 32)) && (tile < (1ll << 32)) && (s_cols < (1ll << 32));
-    if (vec) {
+    const bool wide = (n % (2 * elems) == 0) && (tile % (2 * elems) == 0) && ((reinterpret_cast<uintptr_t>(x) & 31u) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(y) & 31u) == 0) && (n / (2 * elems) < (1ll << 32)) &&
+                      (tile < (1ll << 32)) && (s_cols < (1ll << 32));
+    const uint64_t wide_total = static_cast<uint64_t>(m) * static_cast<uint64_t>(n / (2 * elems));
+    const uint64_t sms = static_cast<uint64_t>(num_sms());
+    if (wide && wide_total >= sms * kThreads * 2) {
+        const bool deep = wide_total >= 2 * sms * kThreads * kWideUnroll;
+        const unsigned grid = grid_for(wide_total, kThreads, deep ? kWideUnroll : 2);
+        auto kern = deep ? (dtype == TB200_DT_F32 ? tb200_k_weight_dequant_f32_wide
+                            : dtype == TB200_DT_F16 ? tb200_k_weight_dequant_f16_wide : tb200_k_weight_dequant_bf16_wide)
+                         : (dtype == TB200_DT_F32 ? tb200_k_weight_dequant_f32_wide2
+                            : dtype == TB200_DT_F16 ? tb200_k_weight_dequant_f16_wide2 : tb200_k_weight_dequant_bf16_wide2);
+        kern<<<grid, kThreads, 0, st>>>(static_cast<const uint8_t*>(x), s, static_cast<uint8_t*>(y),
+                                        static_cast<uint32_t>(n / (2 * elems)), static_cast<uint32_t>(tile / (2 * elems)),
+                                        static_cast<uint32_t>(tile), static_cast<uint32_t>(s_cols), wide_total);
+    } else if (vec) {
         uint64_t total = static_cast<uint64_t>(m) * static_cast<uint64_t>(n / elems);
         unsigned grid = grid_for(total, kThreads, kUnroll);
         auto kern = dtype == TB200_DT_F32 ? tb200_k_weight_dequant_f32
