@@ -45,7 +45,7 @@ FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 # DRAM bytes per launch of tb200_k_dequant_int8_rowwise_bf16 on the headline workload, from one ncu
 # capture (dram__bytes_read.sum + dram__bytes_write.sum).
-NCU_DRAM_BYTES_PER_LAUNCH = 752_797_696   # 268.73 MB read + 484.07 MB written (profiles/dequant_int8_rowwise_bf16_65536x4096.md)
+NCU_DRAM_BYTES_PER_LAUNCH = 753_666_304   # 268.73 MB read + 484.93 MB written (profiles/dequant_int8_rowwise_bf16_wide_65536x4096.md)
 
 
 def load_peaks():
