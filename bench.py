@@ -267,6 +267,34 @@ def sections(torch, dev, peaks, world, rank, steps, warmup):
                               note=f"{sets} rotating sets"))
         del ins
 
+    # ---- the reference's own GEMM operators on the path, at the largest case of their grids ----
+    # matmul_int8: a int8 [2048, 20480] x b uint8 [5120, 2048] (four 2-bit weights per byte) -> int32
+    M, N, K = 2048, 2048, 20480
+    nbytes = M * K + K * N // 4 + 4 * M * N
+    sets = max(2, -(-2 * L2 // nbytes))
+    ai = [torch.randint(-64, 65, (M, K), dtype=torch.int8, device=dev, generator=gen) for _ in range(sets)]
+    bi = [torch.randint(0, 256, (K // 4, N), dtype=torch.uint8, device=dev, generator=gen) for _ in range(sets)]
+    oi = [torch.empty(M, N, dtype=torch.int32, device=dev) for _ in range(sets)]
+    ms = time_rotating(torch, lambda i: (lambda: ext.matmul_int8_packed2(ai[i], bi[i], oi[i])), sets, warmup, iters)
+    out.append(tensor_row("matmul_int8 M=2048 N=2048 K=20480", 2 * M * N * K, ms, 2 * peaks["bf16_tflops"],
+                          f"2 x bf16 cuBLAS burst ({peaks['source']}); no int8 peak was measured", nbytes,
+                          note=f"{sets} rotating sets; TOPS reported as TFLOPs"))
+    del ai, bi, oi
+    # matmul_fp32_fp16_fp8: a [4096, 16384] x b [16384, 4096], both row-major
+    M, N, K = 4096, 4096, 16384
+    for dt, label, peak_mult in ((torch.float16, "fp16", 1.0), (torch.float32, "fp32 (TF32)", 0.5), (torch.float8_e4m3fn, "e4m3", 2.0)):
+        esize = torch.empty((), dtype=dt).element_size()
+        nbytes = (M * K + K * N + M * N) * esize
+        sets = max(2, -(-2 * L2 // nbytes))
+        scale = K ** -0.5
+        ap = [(torch.randn(M, K, device=dev, generator=gen) * scale).to(dt) for _ in range(sets)]
+        bp = [(torch.randn(K, N, device=dev, generator=gen) * scale).to(dt) for _ in range(sets)]
+        op = [torch.empty(M, N, dtype=dt, device=dev) for _ in range(sets)]
+        ms = time_rotating(torch, lambda i: (lambda: ext.matmul_plain(ap[i], bp[i], op[i])), sets, warmup, iters)
+        out.append(tensor_row(f"matmul_fp32_fp16_fp8 {label} M=4096 N=4096 K=16384", 2 * M * N * K, ms, peak_mult * peaks["bf16_tflops"],
+                              f"{peak_mult:g} x bf16 cuBLAS burst ({peaks['source']})", nbytes, note=f"{sets} rotating sets"))
+        del ap, bp, op
+
     # ---- config 4: N-partitioned W4A16 GEMM M=4096 K=8192 N=57344 over `world` ranks ----
     M, K, N = 4096, 8192, 57344
     lo, hi = npart.partition(N, world, rank)
