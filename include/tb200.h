@@ -98,6 +98,16 @@ int tb200_weight_dequant_block(const void* x, const void* s, void* y,
 int tb200_quantize_fp8_block(const float* x, void* q, float* scales, int64_t rows, int64_t cols,
                              int block_rows, void* stream);
 
+/*
+ * int4 group quantiser — the step before tb200_dequant_int4_group / tb200_gemm_w4a16 (no counterpart in the
+ * reference, whose quantiser operator is a plain cast, tilebench/benchmarks/operators/quantize_global/impl_torch.py:4-5).
+ *   x fp32 [n, k]  ->  wp uint8 [n, k/2] (low nibble = even k), scales fp16 [n, k/128]
+ *   s = fp16(amax / 7) per group of 128 (1 where that rounds to zero), q = clamp(rint(x / s) + 8, 0, 15)
+ * group must be 128 and zero_point 8.  Bit-exact against the same formula in PyTorch.
+ */
+int tb200_quantize_int4_group(const float* x, void* wp, void* scales, int64_t n, int64_t k, int64_t group,
+                              int zero_point, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Quantised GEMMs on tcgen05 tensor cores (TMA operands, TMEM accumulators).
  * ------------------------------------------------------------------------------------------- */

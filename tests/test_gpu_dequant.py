@@ -210,3 +210,33 @@ def test_fp8_block_quantiser_bit_exact(cuda_device, rows, cols, block_rows):
     assert torch.equal(s.cpu(), s_ref)
     assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
     assert q.cpu().float().abs().max() == 448.0
+
+
+# ---------------------------------------------------------------- int4 group quantiser
+
+@pytest.mark.parametrize("N,K", [(1, 128), (3, 384), (64, 4096), (4096, 4096)])
+def test_int4_group_quantiser_bit_exact_and_round_trip(cuda_device, N, K):
+    from tilebench_b200.benchmarks.operators.quantize_int4_group import impl_cuda, impl_torch
+    from tilebench_b200.benchmarks.operators.dequant_int4_group import impl_cuda as dequant
+    x, group, zp = tensors.generate_quantize_int4_group_inputs(N, K, device="cpu", seed=N + K)
+    x[0, :128] = 0.0                                        # an all-zero group: scale 1, codes = zero point
+    if K > 128:
+        x[0, 128] = 3.0                                     # one outlier sets its group's scale
+    wp, sc = impl_cuda.run(x.to(cuda_device), group, zp)
+    torch.cuda.synchronize()
+    owp, osc = ref_ops.quantize_int4_group(x.numpy(), group, zp)
+    assert np.array_equal(wp.cpu().numpy(), owp)
+    assert np.array_equal(sc.cpu().numpy().view(np.uint16), osc.view(np.uint16))
+    twp, tsc = impl_torch.run(x.to(cuda_device), group, zp)            # the same formula evaluated by PyTorch on the GPU
+    assert torch.equal(wp, twp) and torch.equal(sc.view(torch.int16), tsc.view(torch.int16))
+    back = dequant.run(wp, sc, group, zp).float().cpu()
+    step = sc.float().cpu().repeat_interleave(group, dim=1)
+    assert torch.all((x - back).abs() <= 0.51 * step)       # half a step + fp16 rounding of (q - zp) * s
+
+
+def test_int4_group_quantiser_rejects_other_groups(cuda_device):
+    ext = native.load()
+    x = torch.zeros(4, 256, device=cuda_device)
+    with pytest.raises(Exception):
+        ext.quantize_int4_group(x, torch.empty(4, 128, dtype=torch.uint8, device=cuda_device),
+                                torch.empty(4, 4, dtype=torch.float16, device=cuda_device), 64, 8)

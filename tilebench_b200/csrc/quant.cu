@@ -3,11 +3,14 @@
 // Streaming and HBM-bound: 4 B read, 1 B written per element.
 //   tb200_k_quant_fp8_1x128     one warp per 1 x 128 block (activations): 4 elements per lane
 //   tb200_k_quant_fp8_128x128   one CTA per 128 x 128 block (weights): 128 threads, one column strip each
+//   tb200_k_quant_int4_g128     int4 group packing (the producer of the int4 dequant / W4A16 operands): half a
+//                               warp per group of 128, 256-bit loads
 // Every operation is an IEEE fp32 one (division by __fdiv_rn), so the result is bit-identical to the
 // same formula evaluated with PyTorch ops.
 #include "common.cuh"
 
 #include <cuda_fp8.h>
+#include <cuda_fp16.h>
 
 namespace tb200 {
 namespace {
@@ -73,6 +76,53 @@ tb200_k_quant_fp8_128x128(const float* __restrict__ x, uint8_t* __restrict__ q, 
     if (threadIdx.x == 0) scales[static_cast<int64_t>(blockIdx.y) * gridDim.x + blockIdx.x] = s;
 }
 
+// int4 group quantiser, group = 128, zero point 8:  s = fp16(amax / 7) (1 if that is zero),
+// q = clamp(rint(x / float(s)) + 8, 0, 15), two values per byte with the even k in the low nibble —
+// the layout tb200_dequant_int4_group and tb200_gemm_w4a16 read.  Each lane loads 8 consecutive floats
+// (one 256-bit load); 16 lanes cover one group, so a warp quantises two consecutive groups per pass and
+// writes 2 x 64 packed bytes.  IEEE division and rint: bit-identical to the same formula in PyTorch.
+extern "C" __global__ void __launch_bounds__(256)
+tb200_k_quant_int4_g128(const float* __restrict__ x, uint32_t* __restrict__ wp, __half* __restrict__ scales,
+                        int64_t total_groups) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+    const int64_t pairs = (total_groups + 1) / 2;
+    for (int64_t pr = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); pr < pairs; pr += warps) {
+        const int64_t grp = 2 * pr + (lane >> 4);
+        const bool valid = grp < total_groups;                  // odd group count: the upper half-warp idles once
+        float v[8];
+        if (valid) {
+            uint32_t r[8];
+            asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                         : "l"(x + grp * 128 + (lane & 15) * 8));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // within the half-warp
+        __half s16 = __float2half_rn(__fdiv_rn(amax, 7.0f));
+        if (__half2float(s16) == 0.f) s16 = __float2half_rn(1.0f);
+        const float s = __half2float(s16);
+        uint32_t packed = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float q = fminf(fmaxf(rintf(__fdiv_rn(v[i], s)) + 8.0f, 0.0f), 15.0f);
+            packed |= static_cast<uint32_t>(static_cast<int>(q)) << (4 * i);
+        }
+        if (valid) {
+            wp[grp * 16 + (lane & 15)] = packed;
+            if ((lane & 15) == 0) scales[grp] = s16;
+        }
+    }
+}
+
 extern "C" int tb200_quantize_fp8_block(const float* x, void* q, float* scales, int64_t rows, int64_t cols,
                                         int block_rows, void* stream) {
     clear_error();
@@ -95,6 +145,26 @@ extern "C" int tb200_quantize_fp8_block(const float* x, void* q, float* scales, 
         dim3 grid(static_cast<unsigned>(cols / 128), static_cast<unsigned>(rows / 128));
         tb200_k_quant_fp8_128x128<<<grid, 128, 0, st>>>(x, static_cast<uint8_t*>(q), scales, cols);
     }
+    TB200_CUDA_TRY(cudaGetLastError());
+    return TB200_OK;
+}
+
+extern "C" int tb200_quantize_int4_group(const float* x, void* wp, void* scales, int64_t n, int64_t k, int64_t group,
+                                         int zero_point, void* stream) {
+    clear_error();
+    if (!x || !wp || !scales) return fail(TB200_ERR_ARG, "quantize_int4_group: null pointer");
+    if (n <= 0 || k <= 0) return fail(TB200_ERR_ARG, "quantize_int4_group: non-positive size n=%lld k=%lld", (long long)n, (long long)k);
+    if (group != 128 || zero_point != 8)
+        return fail(TB200_ERR_UNSUPPORTED, "quantize_int4_group: group=%lld zero_point=%d (only 128 / 8 are built)", (long long)group, zero_point);
+    if (k % 128 != 0) return fail(TB200_ERR_ARG, "quantize_int4_group: k=%lld must be a multiple of the group size 128", (long long)k);
+    if ((reinterpret_cast<uintptr_t>(x) & 31u) || (reinterpret_cast<uintptr_t>(wp) & 3u) || (reinterpret_cast<uintptr_t>(scales) & 1u))
+        return fail(TB200_ERR_ALIGN, "quantize_int4_group: x must be 32-byte, wp 4-byte and scales 2-byte aligned");
+    const int64_t groups = n * (k / 128);
+    int64_t grid = ((groups + 1) / 2 + 7) / 8;
+    const int64_t cap = static_cast<int64_t>(num_sms()) * 8;
+    if (grid > cap) grid = cap;
+    tb200_k_quant_int4_g128<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, static_cast<uint32_t*>(wp), static_cast<__half*>(scales), groups);
     TB200_CUDA_TRY(cudaGetLastError());
     return TB200_OK;
 }

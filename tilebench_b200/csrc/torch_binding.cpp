@@ -191,6 +191,18 @@ void matmul_plain(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor&
              "tb200_matmul_plain");
 }
 
+void quantize_int4_group(const torch::Tensor& x, torch::Tensor& wp, torch::Tensor& scales, int64_t group, int64_t zero_point) {
+    check_cuda(x, "x", torch::kFloat32);
+    check_cuda(wp, "wp", torch::kUInt8);
+    check_cuda(scales, "scales", torch::kFloat16);
+    TORCH_CHECK(x.dim() == 2 && wp.dim() == 2 && wp.size(0) == x.size(0) && wp.size(1) * 2 == x.size(1), "x [n,k], wp [n,k/2]");
+    TORCH_CHECK(group > 0 && scales.dim() == 2 && scales.size(0) == x.size(0) && scales.size(1) * group == x.size(1), "scales must be [n, k/group]");
+    c10::cuda::CUDAGuard guard(x.device());
+    check_rc(tb200_quantize_int4_group(x.data_ptr<float>(), wp.data_ptr(), scales.data_ptr(), x.size(0), x.size(1), group,
+                                       static_cast<int>(zero_point), stream_of(x)),
+             "tb200_quantize_int4_group");
+}
+
 py::tuple device_status() {
     int code = 0, detail = 0;
     check_rc(tb200_device_status(&code, &detail), "tb200_device_status");
@@ -216,6 +228,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("quantize_fp8_block", &quantize_fp8_block);
     m.def("matmul_int8_packed2", &matmul_int8_packed2);
     m.def("matmul_plain", &matmul_plain);
+    m.def("quantize_int4_group", &quantize_int4_group);
     m.def("device_status", &device_status);
     m.def("clear_device_status", &clear_device_status);
 }

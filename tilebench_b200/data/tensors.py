@@ -122,6 +122,25 @@ def generate_gemm_w4a16_npart_inputs(M, K, N, WORLD=1, GATHER=1, GROUP=128, ZP=8
     return (a, wp, scales, group, zp, WORLD, GATHER)
 
 
+def quantize_int4_groupwise(x: torch.Tensor, group: int = 128, zp: int = 8):
+    """int4 group quantisation: s = fp16(amax / 7) per group (1 where that rounds to zero),
+    q = clamp(round(x / s) + zp, 0, 15), two values per byte with the even k in the low nibble.
+    Returns (wp uint8 [N, K/2], scales fp16 [N, K/group])."""
+    n, k = x.shape
+    xg = x.reshape(n, k // group, group).to(torch.float32)
+    amax = xg.abs().amax(dim=2)
+    s16 = (amax / torch.full_like(amax, 7.0)).to(torch.float16)          # tensor / tensor: a true IEEE division
+    s16 = torch.where(s16.float() == 0, torch.ones_like(s16), s16)
+    q = (torch.round(xg / s16.float()[:, :, None]) + float(zp)).clamp(0, 15).to(torch.uint8).reshape(n, k)
+    return q[:, 0::2] | (q[:, 1::2] << 4), s16
+
+
+def generate_quantize_int4_group_inputs(N, K, GROUP=128, ZP=8, dtype=torch.float32, device=DEFAULT_DEVICE,
+                                        seed=SEED0 + 9000, **kwargs):
+    x = torch.randn(N, K, generator=_gen(seed)) * 0.05
+    return (x.to(device), int(GROUP), int(ZP))
+
+
 def generate_quantize_fp8_block_inputs(S, BLOCK_ROWS=1, dtype=torch.float32, device=DEFAULT_DEVICE,
                                        seed=SEED0 + 7000, **kwargs):
     x = torch.randn(S, S, generator=_gen(seed))
@@ -174,6 +193,7 @@ GENERATORS = {
     "gemm_fp8_blockscaled": generate_gemm_fp8_blockscaled_inputs,
     "gemm_w4a16_npart": generate_gemm_w4a16_npart_inputs,
     "quantize_fp8_block": generate_quantize_fp8_block_inputs,
+    "quantize_int4_group": generate_quantize_int4_group_inputs,
     "dequantize_rowwise": generate_dequantize_rowwise_inputs,
     "weight_dequant": generate_weight_dequant_inputs,
     "matmul_int8": generate_matmul_int8_inputs,
@@ -203,6 +223,8 @@ def infer_problem_size(operator_name, params):
         return int(p.get("M") or s) * int(p.get("N") or s)
     if operator_name == "quantize_fp8_block":
         return int(p["S"]) ** 2
+    if operator_name == "quantize_int4_group":
+        return int(p["N"]) * int(p["K"])
     if operator_name == "weight_dequant":
         return int(p["M"]) * int(p.get("N") or p["M"])
     if operator_name in ("matmul_int8", "matmul_fp32_fp16_fp8"):

@@ -22,7 +22,7 @@ ABI_SYMBOLS = (
     "tb200_gemm_fp8_blockscaled", "tb200_gemm_w4a16_workspace_bytes", "tb200_gemm_w4a16",
     "tb200_device_status", "tb200_clear_device_status",
     "tb200_gemm_w4a16_static_scratch_bytes", "tb200_gemm_w4a16_static", "tb200_gemm_w4a16_gather",
-    "tb200_quantize_fp8_block", "tb200_matmul_int8_packed2", "tb200_matmul_plain",
+    "tb200_quantize_fp8_block", "tb200_matmul_int8_packed2", "tb200_matmul_plain", "tb200_quantize_int4_group",
 )
 
 DT_F32, DT_F16, DT_BF16, DT_F8E4M3 = 0, 1, 2, 3
@@ -93,6 +93,8 @@ def capi() -> ctypes.CDLL:
     lib.tb200_matmul_int8_packed2.restype = ci
     lib.tb200_matmul_plain.argtypes = [vp, vp, vp, i64, i64, i64, ci, i64, vp]
     lib.tb200_matmul_plain.restype = ci
+    lib.tb200_quantize_int4_group.argtypes = [vp, vp, vp, i64, i64, i64, ci, vp]
+    lib.tb200_quantize_int4_group.restype = ci
     lib.tb200_device_status.argtypes = [ctypes.POINTER(ci), ctypes.POINTER(ci)]
     lib.tb200_clear_device_status.argtypes = []
     for name in ("tb200_dequant_int4_group", "tb200_dequant_int8_rowwise", "tb200_weight_dequant_block",
