@@ -240,3 +240,21 @@ def test_int4_group_quantiser_rejects_other_groups(cuda_device):
     with pytest.raises(Exception):
         ext.quantize_int4_group(x, torch.empty(4, 128, dtype=torch.uint8, device=cuda_device),
                                 torch.empty(4, 4, dtype=torch.float16, device=cuda_device), 64, 8)
+
+
+def test_host_buffer_pipeline_matches_the_device_operator(cuda_device):
+    # chunked upload / kernel / download over three streams must give the same bits as one device call,
+    # for a row count that is not a multiple of the chunk and with the staging slots reused several times
+    from tilebench_b200 import host_api
+    from tilebench_b200.benchmarks.operators.dequant_int8_channel import impl_cuda
+    rows, cols = 5000, 1024
+    w, scale = tensors.generate_dequant_int8_channel_inputs(rows, cols, device="cpu", seed=11)
+    hw, hs = w.pin_memory(), scale.pin_memory()
+    hout = torch.empty((rows, cols), dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):                                       # second call reuses the cached staging buffers
+        host_api.dequant_int8_channel_host(hw, hs, hout, device=cuda_device, chunk_rows=384, depth=3)
+        torch.cuda.synchronize()
+        want = impl_cuda.run(w.to(cuda_device), scale.to(cuda_device)).cpu()
+        assert torch.equal(hout.view(torch.int16), want.view(torch.int16))
+    with pytest.raises(ValueError):
+        host_api.dequant_int8_channel_host(w.to(cuda_device), hs, hout)
