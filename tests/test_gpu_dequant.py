@@ -258,3 +258,56 @@ def test_host_buffer_pipeline_matches_the_device_operator(cuda_device):
         assert torch.equal(hout.view(torch.int16), want.view(torch.int16))
     with pytest.raises(ValueError):
         host_api.dequant_int8_channel_host(w.to(cuda_device), hs, hout)
+
+
+# ---------------------------------------------------------------- wide (256-bit) vs narrow kernel dispatch
+
+def _offset_copy(t, byte_offset):
+    """The same values in a fresh allocation whose data pointer is `byte_offset` bytes past a 256-byte boundary."""
+    flat = torch.empty(t.numel() * t.element_size() + byte_offset, dtype=torch.uint8, device=t.device)
+    view = flat[byte_offset:].view(t.dtype).view(t.shape)
+    view.copy_(t)
+    return view
+
+
+@pytest.mark.parametrize("rows,cols", [(2048, 4096), (8192, 4096), (4096, 4104), (3000, 4128)])
+def test_int8_wide_and_narrow_kernels_agree(cuda_device, rows, cols):
+    # 32-byte aligned operands take the 256-bit kernels (deep or two-chunk variant by size), operands that are
+    # only 16-byte aligned, or whose rows are not a multiple of 32, take the 128-bit kernel: same bits either way
+    ext = native.load()
+    w, scale = tensors.generate_dequant_int8_channel_inputs(rows, cols, device=cuda_device, seed=rows + cols)
+    want = ref_ops.dequant_int8_channel(w.cpu().numpy(), scale.cpu().numpy())
+    for w_off, o_off in ((0, 0), (16, 0), (0, 16), (8, 16)):
+        wv = _offset_copy(w, w_off)
+        out = _offset_copy(torch.zeros(rows, cols, dtype=torch.bfloat16, device=cuda_device), o_off)
+        ext.dequant_int8_rowwise(wv, scale, out, False, 1.0)
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().view(torch.int16).numpy().view(np.uint16), want), (w_off, o_off)
+
+
+@pytest.mark.parametrize("N,K", [(4096, 4096), (512, 1024), (1024, 4224)])
+def test_int4_wide_and_narrow_kernels_agree(cuda_device, N, K):
+    ext = native.load()
+    wp, sc, group, zp = tensors.generate_dequant_int4_group_inputs(N, K, device=cuda_device, seed=N + K)
+    want = ref_ops.dequant_int4_group(wp.cpu().numpy(), sc.cpu().numpy(), group, zp)
+    for w_off, o_off in ((0, 0), (4, 0), (0, 16)):
+        wv = _offset_copy(wp, w_off)
+        out = _offset_copy(torch.zeros(N, K, dtype=torch.float16, device=cuda_device), o_off)
+        ext.dequant_int4_group(wv, sc, out, group, zp)
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy().view(np.uint16), want.view(np.uint16)), (w_off, o_off)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_weight_dequant_wide_and_narrow_kernels_agree(cuda_device, dtype):
+    from tilebench_b200.benchmarks.operators.weight_dequant import impl_torch
+    ext = native.load()
+    M = N = 2048
+    X, S, _, _, T = tensors.generate_weight_dequant_inputs(M, 128, dtype, device=cuda_device, seed=77)
+    want = impl_torch.run(X, S, M, N, T)
+    for x_off, y_off in ((0, 0), (16, 0), (0, 16)):
+        xv = _offset_copy(X, x_off)
+        y = _offset_copy(torch.zeros(M, N, dtype=dtype, device=cuda_device), y_off)
+        ext.weight_dequant_block(xv, S, y, M, N, T)
+        torch.cuda.synchronize()
+        assert torch.equal(y.view(torch.uint8), want.view(torch.uint8)), (x_off, y_off)
