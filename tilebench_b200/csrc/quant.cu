@@ -1,7 +1,7 @@
 // FP8 e4m3 block quantiser (the step before the block-scaled GEMM): per [block_rows x 128] block
 // scale = amax / 448 (1 for an all-zero block), q = e4m3(clamp(x / scale, +-448)), round to nearest even.
 // Streaming and HBM-bound: 4 B read, 1 B written per element.
-//   tb200_k_quant_fp8_1x128     one warp per 1 x 128 block (activations): 4 elements per lane
+//   tb200_k_quant_fp8_1x128     half a warp per 1 x 128 block (activations): 8 elements per lane, 256-bit loads
 //   tb200_k_quant_fp8_128x128   one CTA per 128 x 128 block (weights): 128 threads, one column strip each
 //   tb200_k_quant_int4_g128     int4 group packing (the producer of the int4 dequant / W4A16 operands): half a
 //                               warp per group of 128, 256-bit loads
@@ -28,21 +28,44 @@ __device__ __forceinline__ float clamp448(float v) { return fminf(fmaxf(v, -kFp8
 
 using namespace tb200;
 
+// Half a warp per 1 x 128 block: each lane loads 8 consecutive floats with one 256-bit load and stores its
+// 8 codes with one 64-bit store, so a warp quantises two consecutive blocks per pass.
 extern "C" __global__ void __launch_bounds__(256)
-tb200_k_quant_fp8_1x128(const float4* __restrict__ x, uint32_t* __restrict__ q, float* __restrict__ scales,
+tb200_k_quant_fp8_1x128(const float* __restrict__ x, uint2* __restrict__ q, float* __restrict__ scales,
                         int64_t total_blocks) {
     const int lane = threadIdx.x & 31;
     const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
-    for (int64_t blk = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); blk < total_blocks;
-         blk += warps) {
-        const float4 v = __ldg(x + blk * 32 + lane);
-        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    const int64_t pairs = (total_blocks + 1) / 2;
+    for (int64_t pr = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); pr < pairs; pr += warps) {
+        const int64_t blk = 2 * pr + (lane >> 4);
+        const bool valid = blk < total_blocks;                  // odd block count: the upper half-warp idles once
+        float v[8];
+        if (valid) {
+            uint32_t r[8];
+            asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                         : "l"(x + blk * 128 + (lane & 15) * 8));
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // within the half-warp
         const float s = amax > 0.f ? __fdiv_rn(amax, kFp8Max) : 1.0f;
-        q[blk * 32 + lane] = pack_e4m3x4(clamp448(__fdiv_rn(v.x, s)), clamp448(__fdiv_rn(v.y, s)),
-                                         clamp448(__fdiv_rn(v.z, s)), clamp448(__fdiv_rn(v.w, s)));
-        if (lane == 0) scales[blk] = s;
+        uint2 o;
+        o.x = pack_e4m3x4(clamp448(__fdiv_rn(v[0], s)), clamp448(__fdiv_rn(v[1], s)), clamp448(__fdiv_rn(v[2], s)),
+                          clamp448(__fdiv_rn(v[3], s)));
+        o.y = pack_e4m3x4(clamp448(__fdiv_rn(v[4], s)), clamp448(__fdiv_rn(v[5], s)), clamp448(__fdiv_rn(v[6], s)),
+                          clamp448(__fdiv_rn(v[7], s)));
+        if (valid) {
+            q[blk * 16 + (lane & 15)] = o;
+            if ((lane & 15) == 0) scales[blk] = s;
+        }
     }
 }
 
@@ -131,15 +154,15 @@ extern "C" int tb200_quantize_fp8_block(const float* x, void* q, float* scales, 
         return fail(TB200_ERR_ARG, "quantize_fp8_block: rows=%lld, cols=%lld (cols must be a positive multiple of 128)", (long long)rows, (long long)cols);
     if (block_rows != 1 && block_rows != 128) return fail(TB200_ERR_UNSUPPORTED, "quantize_fp8_block: block_rows %d (1 or 128)", block_rows);
     if (block_rows == 128 && rows % 128 != 0) return fail(TB200_ERR_ARG, "quantize_fp8_block: rows=%lld must be a multiple of 128 for 128x128 blocks", (long long)rows);
-    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 3u)) return fail(TB200_ERR_ALIGN, "quantize_fp8_block: x must be 16-byte and q 4-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(x) & 31u) || (reinterpret_cast<uintptr_t>(q) & 7u))
+        return fail(TB200_ERR_ALIGN, "quantize_fp8_block: x must be 32-byte and q 8-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (block_rows == 1) {
         const int64_t blocks = rows * (cols / 128);
-        int64_t grid = (blocks + 7) / 8;
+        int64_t grid = ((blocks + 1) / 2 + 7) / 8;
         const int64_t cap = static_cast<int64_t>(num_sms()) * 8;
         if (grid > cap) grid = cap;
-        tb200_k_quant_fp8_1x128<<<static_cast<unsigned>(grid), 256, 0, st>>>(reinterpret_cast<const float4*>(x),
-                                                                              static_cast<uint32_t*>(q), scales, blocks);
+        tb200_k_quant_fp8_1x128<<<static_cast<unsigned>(grid), 256, 0, st>>>(x, static_cast<uint2*>(q), scales, blocks);
     } else {
         if (cols / 128 > 0x7fffffff || rows / 128 > 65535) return fail(TB200_ERR_UNSUPPORTED, "quantize_fp8_block: matrix too large");
         dim3 grid(static_cast<unsigned>(cols / 128), static_cast<unsigned>(rows / 128));
