@@ -141,12 +141,12 @@ int tb200_matmul_int8_packed2(const void* a, const void* b, void* out, int64_t m
  * Plain GEMM out = a . b — the reference operator `matmul_fp32_fp16_fp8`
  * (tilebench/benchmarks/operators/matmul_fp32_fp16_fp8/impl_torch.py:21-27; generator
  * tilebench/data/tensors.py:416-436).  a [m, k] and b [k, n] row-major and of one type, out [m, ldo]:
- *   TB200_DT_F16     fp16 in, fp32 accumulation, fp16 out
+ *   TB200_DT_F16     fp16 in, fp32 accumulation, fp16 out   (TB200_DT_BF16 likewise, bf16 out)
  *   TB200_DT_F32     fp32 in, read by the tensor cores as TF32 (the reference sets allow_tf32), fp32 out
  *   TB200_DT_F8E4M3  e4m3 in, unit scales, fp32 accumulation, out e4m3 = e4m3(bf16(sum)) as the reference's
  *                    _scaled_mm(out_dtype=bfloat16) followed by a cast gives; overflow becomes NaN as in PyTorch
  * b is consumed as stored (an MN-major tensor-core operand): no transposed copy is made or cached.
- * n a multiple of 128; k a multiple of 64 (fp16), 32 (fp32) or 128 (e4m3); a, b, out and the rows of out
+ * n a multiple of 128; k a multiple of 64 (fp16, bf16), 32 (fp32) or 128 (e4m3); a, b, out and the rows of out
  * 16-byte aligned.
  */
 int tb200_matmul_plain(const void* a, const void* b, void* out, int64_t m, int64_t n, int64_t k, int dtype,

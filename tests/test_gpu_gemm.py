@@ -367,4 +367,15 @@ def test_plain_rejects_unsupported(cuda_device):
     with pytest.raises(Exception):
         impl_cuda.run(a, torch.zeros(100, 128, dtype=torch.float16, device=cuda_device))
     with pytest.raises(NotImplementedError):
-        impl_cuda.run(a.to(torch.bfloat16), torch.zeros(100, 128, dtype=torch.bfloat16, device=cuda_device))
+        impl_cuda.run(a.to(torch.float64), torch.zeros(100, 128, dtype=torch.float64, device=cuda_device))
+
+
+@pytest.mark.parametrize("M,N,K", [(100, 256, 512), (2048, 2048, 1024)])
+def test_plain_bf16_matches_fp32_reference(cuda_device, M, N, K):
+    a, b = tensors.generate_matmul_fp32_fp16_fp8_inputs(M, N, K, dtype=torch.bfloat16, device="cpu", seed=M + K)
+    got = plain_run(a.to(cuda_device), b.to(cuda_device)).float().cpu().numpy()
+    want = ref_ops.bf16_bits_to_f32(ref_ops.f32_to_bf16_bits(ref_ops.matmul_f32(a.float().numpy(), b.float().numpy())))
+    np.testing.assert_allclose(got, want, atol=1e-2, rtol=1.6e-2)          # bf16 tolerance of the reference's verifier
+    eye = torch.eye(512, dtype=torch.bfloat16, device=cuda_device)
+    bb = torch.randint(-8, 9, (512, 256), dtype=torch.int32).to(torch.bfloat16).to(cuda_device)
+    assert torch.equal(plain_run(eye, bb), bb)

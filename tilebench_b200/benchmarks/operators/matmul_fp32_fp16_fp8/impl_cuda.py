@@ -5,13 +5,13 @@ import torch
 
 from tilebench_b200 import native
 
-_SUPPORTED = (torch.float32, torch.float16, torch.float8_e4m3fn)
+_SUPPORTED = (torch.float32, torch.float16, torch.bfloat16, torch.float8_e4m3fn)
 
 
 def run(a: torch.Tensor, b: torch.Tensor, block_size=None, autotune: bool = False, **kwargs):
     ext = native.load()
     if a.dtype != b.dtype or a.dtype not in _SUPPORTED:
-        raise NotImplementedError(f"matmul_fp32_fp16_fp8 cuda backend supports float32, float16 and float8_e4m3fn, got {a.dtype} x {b.dtype}")
+        raise NotImplementedError(f"matmul_fp32_fp16_fp8 cuda backend supports float32, float16, bfloat16 and float8_e4m3fn, got {a.dtype} x {b.dtype}")
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:
         raise ValueError(f"shapes {tuple(a.shape)} x {tuple(b.shape)} do not form a GEMM")
     out = torch.empty((a.shape[0], b.shape[1]), dtype=a.dtype, device=a.device)

@@ -1,7 +1,7 @@
 // Plain GEMM out[M, N] = a[M, K] . b[K, N] for the reference operator matmul_fp32_fp16_fp8
 // (tilebench/benchmarks/operators/matmul_fp32_fp16_fp8/impl_torch.py:21-27), both operands row-major as
 // the reference's generator makes them (tilebench/data/tensors.py:416-436):
-//   fp16  x fp16  -> fp16   tcgen05 kind::f16,    fp32 accumulation
+//   fp16  x fp16  -> fp16   tcgen05 kind::f16,    fp32 accumulation   (bf16 x bf16 -> bf16 likewise)
 //   fp32  x fp32  -> fp32   tcgen05 kind::tf32 (the reference sets allow_tf32), fp32 accumulation
 //   e4m3  x e4m3  -> e4m3   tcgen05 kind::f8f6f4, fp32 accumulation, rounded to bf16 and then to e4m3 as the
 //                           reference does (_scaled_mm with unit scales and out_dtype bf16, then a cast)
@@ -27,13 +27,18 @@ constexpr int kPlBM = 128;
 constexpr int kPlStages = 4;
 constexpr int kPlGroupM = 16;
 
-enum PlainKind : int { PK_F16 = 0, PK_TF32 = 1, PK_F8 = 2 };
+enum PlainKind : int { PK_F16 = 0, PK_TF32 = 1, PK_F8 = 2, PK_BF16 = 3 };
 
 template <int KIND> struct PlainTraits;
 template <> struct PlainTraits<PK_F16> {
     using In = __half;
     using Out = __half;
     static constexpr int kFmt = 0;          // f16
+};
+template <> struct PlainTraits<PK_BF16> {
+    using In = __nv_bfloat16;
+    using Out = __nv_bfloat16;
+    static constexpr int kFmt = 1;          // bf16
 };
 template <> struct PlainTraits<PK_TF32> {
     using In = float;
@@ -83,7 +88,7 @@ __host__ __device__ constexpr uint32_t pl_idesc(uint32_t fmt, uint32_t m, uint32
 }
 template <int KIND>
 __device__ __forceinline__ void pl_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    if constexpr (KIND == PK_F16) {
+    if constexpr (KIND == PK_F16 || KIND == PK_BF16) {
         asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
                      "r"(idesc), "r"(accumulate) : "memory");
@@ -100,7 +105,7 @@ __device__ __forceinline__ void pl_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
 
 template <int KIND>
 __device__ __forceinline__ void pl_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    if constexpr (KIND == PK_F16) {
+    if constexpr (KIND == PK_F16 || KIND == PK_BF16) {
         asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
                      "r"(idesc), "r"(accumulate) : "memory");
@@ -134,6 +139,19 @@ __device__ __forceinline__ void pl_store32(__half* dst, const uint32_t (&v)[32])
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             __half2 h = __floats2half2_rn(__uint_as_float(v[8 * q + 2 * e]), __uint_as_float(v[8 * q + 2 * e + 1]));
+            w[e] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(dst + 8 * q) = o;
+    }
+}
+__device__ __forceinline__ void pl_store32(__nv_bfloat16* dst, const uint32_t (&v)[32]) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        uint4 o;
+        uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * e]), __uint_as_float(v[8 * q + 2 * e + 1]));
             w[e] = *reinterpret_cast<uint32_t*>(&h);
         }
         *reinterpret_cast<uint4*>(dst + 8 * q) = o;
@@ -496,6 +514,7 @@ __device__ __forceinline__ void gemm_plain_pair_body(const CUtensorMap* __restri
 TB200_PLAIN_PAIR_KERNEL(tb200_k_gemm_f16_pair, PK_F16)
 TB200_PLAIN_PAIR_KERNEL(tb200_k_gemm_tf32_pair, PK_TF32)
 TB200_PLAIN_PAIR_KERNEL(tb200_k_gemm_f8_pair, PK_F8)
+TB200_PLAIN_PAIR_KERNEL(tb200_k_gemm_bf16_pair, PK_BF16)
 
 #define TB200_PLAIN_KERNEL(name, KIND, BN)                                                                              \
     extern "C" __global__ void __launch_bounds__(256, 1)                                                                \
@@ -509,6 +528,8 @@ TB200_PLAIN_KERNEL(tb200_k_gemm_tf32_n256, PK_TF32, 256)
 TB200_PLAIN_KERNEL(tb200_k_gemm_tf32_n128, PK_TF32, 128)
 TB200_PLAIN_KERNEL(tb200_k_gemm_f8_n256, PK_F8, 256)
 TB200_PLAIN_KERNEL(tb200_k_gemm_f8_n128, PK_F8, 128)
+TB200_PLAIN_KERNEL(tb200_k_gemm_bf16_n256, PK_BF16, 256)
+TB200_PLAIN_KERNEL(tb200_k_gemm_bf16_n128, PK_BF16, 128)
 
 TB200_DEFINE_STATUS_HOOKS(gemm_plain)
 
@@ -524,6 +545,7 @@ static int launch_plain(Kern kern, const void* a, const void* b, void* out, int6
         attr_set[dev] = true;
     }
     const CUtensorMapDataType dt = KIND == PK_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                 : KIND == PK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                  : KIND == PK_TF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     CUtensorMap ta, tb;
     int rc = encode_tmap_2d(&ta, a, dt, Cfg::kElem, m, k, k * Cfg::kElem, kPlBM, Cfg::kBK, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -560,6 +582,7 @@ static int launch_plain_pair(Kern kern, const void* a, const void* b, void* out,
         max_pairs[dev] = clusters;
     }
     const CUtensorMapDataType dt = KIND == PK_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                 : KIND == PK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                  : KIND == PK_TF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     CUtensorMap ta, tb;
     int rc = encode_tmap_2d(&ta, a, dt, Cfg::kElem, m, k, k * Cfg::kElem, kPlBM, Cfg::kBK, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -581,9 +604,9 @@ extern "C" int tb200_matmul_plain(const void* a, const void* b, void* out, int64
     if (!a || !b || !out) return fail(TB200_ERR_ARG, "matmul_plain: null pointer");
     if (m <= 0 || n <= 0 || k <= 0)
         return fail(TB200_ERR_ARG, "matmul_plain: non-positive size m=%lld n=%lld k=%lld", (long long)m, (long long)n, (long long)k);
-    if (dtype != TB200_DT_F32 && dtype != TB200_DT_F16 && dtype != TB200_DT_F8E4M3)
-        return fail(TB200_ERR_UNSUPPORTED, "matmul_plain: dtype %d is not one of F32 (tf32 math), F16, F8E4M3", dtype);
-    const int elem = dtype == TB200_DT_F32 ? 4 : (dtype == TB200_DT_F16 ? 2 : 1);
+    if (dtype != TB200_DT_F32 && dtype != TB200_DT_F16 && dtype != TB200_DT_BF16 && dtype != TB200_DT_F8E4M3)
+        return fail(TB200_ERR_UNSUPPORTED, "matmul_plain: dtype %d is not one of F32 (tf32 math), F16, BF16, F8E4M3", dtype);
+    const int elem = dtype == TB200_DT_F32 ? 4 : (dtype == TB200_DT_F8E4M3 ? 1 : 2);
     const int64_t bk = 128 / elem;
     if (k % bk != 0 || n % 128 != 0)
         return fail(TB200_ERR_UNSUPPORTED, "matmul_plain: k=%lld must be a multiple of %lld and n=%lld of 128", (long long)k, (long long)bk, (long long)n);
@@ -601,9 +624,13 @@ extern "C" int tb200_matmul_plain(const void* a, const void* b, void* out, int64
     const bool pair = force ? !strcmp(force, "pair") : 4 * tiles_pair >= num_sms();
     if (pair && n % 256 == 0 && tiles_pair >= 1) {
         if (dtype == TB200_DT_F16) return launch_plain_pair<PK_F16>(tb200_k_gemm_f16_pair, a, b, out, m, n, k, ldo, st);
+        if (dtype == TB200_DT_BF16) return launch_plain_pair<PK_BF16>(tb200_k_gemm_bf16_pair, a, b, out, m, n, k, ldo, st);
         if (dtype == TB200_DT_F32) return launch_plain_pair<PK_TF32>(tb200_k_gemm_tf32_pair, a, b, out, m, n, k, ldo, st);
         return launch_plain_pair<PK_F8>(tb200_k_gemm_f8_pair, a, b, out, m, n, k, ldo, st);
     }
+    if (dtype == TB200_DT_BF16)
+        return wide ? launch_plain<PK_BF16, 256>(tb200_k_gemm_bf16_n256, a, b, out, m, n, k, ldo, st)
+                    : launch_plain<PK_BF16, 128>(tb200_k_gemm_bf16_n128, a, b, out, m, n, k, ldo, st);
     if (dtype == TB200_DT_F16)
         return wide ? launch_plain<PK_F16, 256>(tb200_k_gemm_f16_n256, a, b, out, m, n, k, ldo, st)
                     : launch_plain<PK_F16, 128>(tb200_k_gemm_f16_n128, a, b, out, m, n, k, ldo, st);

@@ -181,8 +181,9 @@ void matmul_plain(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor&
     int dt = -1;
     if (a.scalar_type() == torch::kFloat32) dt = TB200_DT_F32;
     else if (a.scalar_type() == torch::kFloat16) dt = TB200_DT_F16;
+    else if (a.scalar_type() == torch::kBFloat16) dt = TB200_DT_BF16;
     else if (a.scalar_type() == torch::kFloat8_e4m3fn) dt = TB200_DT_F8E4M3;
-    if (dt < 0) throw py::type_error("matmul_plain: dtype must be float32, float16 or float8_e4m3fn");
+    if (dt < 0) throw py::type_error("matmul_plain: dtype must be float32, float16, bfloat16 or float8_e4m3fn");
     TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(0), "a [m,k], b [k,n]");
     TORCH_CHECK(out.dim() == 2 && out.size(0) == a.size(0) && out.size(1) == b.size(1) && out.stride(1) == 1, "out must be [m,n]");
     c10::cuda::CUDAGuard guard(a.device());
