@@ -25,9 +25,9 @@
 //                     fewer cycles than one thread needs to issue them, so decode-sized tiles use
 //                     several issuers; private accumulators keep the summation order fixed.
 //   warps 6..7        idle (keep the following warp quads aligned with the TMEM lane quarters)
-//   warps 8..15       convert warps (two groups of 4 taking alternate K blocks): thread = weight row;
+//   warps 8..         convert warps (kDQ groups of 4 taking K blocks in turn): thread = weight row;
 //                     2 x LDS.128 of packed nibbles -> 64 fp16 -> tcgen05.st into an operand stage
-//   warps 16..19      epilogue: tcgen05.ld the finished accumulators (summed in issuer order), cast;
+//   next 4 warps      epilogue: tcgen05.ld the finished accumulators (summed in issuer order), cast;
 //                     for MT >= 128 transpose
 //                     through a shared-memory tile and write it with one TMA store per 128 rows,
 //                     otherwise store directly (fp32 split-K partials or fp16)
@@ -47,7 +47,11 @@ constexpr int kGroupN = 16;    // tile-order grouping for L2 reuse
 
 // MT = activation rows per work item = MMA N.
 template <int MT> struct W4Cfg {
-    static constexpr int kDQ = 2;                                // convert warp groups (alternate K blocks)
+    // Convert warp groups; group g takes the K blocks with it % kDQ == g.  One group needs about 1 us per K block
+    // (barrier hops, LDS, ~140 dependent ALU instructions, tcgen05.st), so two groups deliver a block every
+    // ~0.5 us whatever the tile size.  That is below the MMA time of the 256-row tile, but it is what bounds
+    // the 128-row tile (m of 65..128, one wave of CTAs): a third group there is worth 10-15 %.
+    static constexpr int kDQ = MT == 128 ? 3 : 2;
     static constexpr int kActStageBytes = MT * kBK * 2;          // one [MT x 64] fp16 activation tile
     static constexpr int kNI = MT <= 32 ? 4 : (MT <= 128 ? 2 : 1);   // MMA issuer threads, one accumulator each
     static constexpr int kNAcc = MT >= 128 ? 1 : 2;              // accumulator sets (double-buffered when they fit)
