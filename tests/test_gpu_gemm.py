@@ -81,7 +81,8 @@ def test_fp8_4096_cube_vs_torch_reference(cuda_device):
 
 
 @pytest.mark.parametrize("variant", ["pair", "n256", "n128"])
-@pytest.mark.parametrize("M,N,K", [(1, 256, 256), (300, 512, 1024), (1000, 1792, 512), (2048, 2048, 2048)])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 256), (300, 512, 1024), (1000, 1792, 512), (2048, 2048, 2048),
+                                   (4096, 4096, 256), (2432, 4096, 256)])      # the last two: split last wave (68 / 8 tiles)
 def test_fp8_kernel_variants_agree_bit_for_bit(cuda_device, monkeypatch, variant, M, N, K):
     # The CTA-pair kernel (one MMA across two SMs), the 128 x 256 and the 128 x 128 kernel add the same
     # scaled K-block products in the same order: their results must be identical, ragged M included.

@@ -57,7 +57,20 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n)
 template <int S, int BN, bool kPair>
 __device__ __forceinline__ bool drain_tile(uint64_t* bar_done, uint64_t* bar_tempty, uint32_t& it, uint32_t t_lane, int KB,
                                            const float* __restrict__ sa_row, const float* __restrict__ sb_row,
-                                           float (&acc)[128], int lane) {
+                                           float (&acc)[128], int lane, bool active = true) {
+    if (!active) {
+        // this warp's half of the accumulator is not part of the current (128-wide) unit: keep the barrier
+        // protocol in step and release each buffer at once
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+            if (!mbar_wait(&bar_done[it % S], (it / S) & 1, ST_WAIT_TMEM_FULL, kb)) return false;
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (kPair) mbar_arrive_leader(&bar_tempty[it & 1]);
+                else mbar_arrive(&bar_tempty[it & 1]);
+            }
+        }
+        return true;
+    }
     // Scales are fetched three K blocks ahead and kept RAW: the product is formed only when it is
     // used, so no instruction that depends on a load in flight sits on the critical path.
     float pa0 = __ldg(sa_row), pb0 = __ldg(sb_row);
@@ -120,8 +133,10 @@ using namespace tb200;
 
 template <int BN>
 __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tmap_a, const CUtensorMap* __restrict__ tmap_b,
+                                              const CUtensorMap* __restrict__ tmap_b128,
                                               const float* __restrict__ sa, const float* __restrict__ sb,
-                                              __nv_bfloat16* __restrict__ out, int M, int N, int K, int64_t ldo) {
+                                              __nv_bfloat16* __restrict__ out, int M, int N, int K, int64_t ldo,
+                                              int wide_units) {
     using Cfg = Fp8Cfg<BN>;
     constexpr int S = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -137,6 +152,20 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
     const int tiles_m = (M + kBM - 1) / kBM;
     const int tiles_n = N / BN;
     const int tiles = tiles_m * tiles_n;
+    // Work units: the first `wide_units` are whole 128 x BN tiles; the tiles after them (the partial last wave
+    // of the persistent grid) are cut into two 128 x 128 units each, so that the tail occupies twice as many
+    // SMs for half as long.
+    const int units = wide_units + 2 * (tiles - wide_units);
+    struct Unit { int m_blk, n_col0, ncols; };
+    auto unit_of = [&](int u) {
+        if (u < wide_units) {
+            const TileCoord tc = tile_coord(u, tiles_m, tiles_n);
+            return Unit{tc.m_blk, tc.n_blk * BN, BN};
+        }
+        const int v = u - wide_units;
+        const TileCoord tc = tile_coord(wide_units + (v >> 1), tiles_m, tiles_n);
+        return Unit{tc.m_blk, tc.n_blk * BN + (v & 1) * 128, 128};
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
@@ -166,16 +195,16 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-                const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                const Unit un = unit_of(u);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % S;
                     const uint32_t ph = (it / S) & 1;
                     if (!mbar_wait(&bar_empty[s], ph ^ 1, ST_WAIT_SMEM_EMPTY, kb)) { ok = false; break; }
                     uint8_t* stage = smem + s * Cfg::kStageBytes;
-                    mbar_expect_tx(&bar_full[s], Cfg::kStageBytes);
-                    tma_load_2d(stage, tmap_a, &bar_full[s], kb * kBK, tc.m_blk * kBM);
-                    tma_load_2d(stage + Cfg::kABytes, tmap_b, &bar_full[s], kb * kBK, tc.n_blk * BN);
+                    mbar_expect_tx(&bar_full[s], Cfg::kABytes + un.ncols * kBK);
+                    tma_load_2d(stage, tmap_a, &bar_full[s], kb * kBK, un.m_blk * kBM);
+                    tma_load_2d(stage + Cfg::kABytes, un.ncols == BN ? tmap_b : tmap_b128, &bar_full[s], kb * kBK, un.n_col0);
                 }
             }
             if (!ok) {
@@ -195,11 +224,13 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
         // two instruction streams are independent; each thread's waits and issue cost (several
         // hundred cycles per K block) overlap the other's.
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc(0, 0, kBM, BN);  // e4m3 x e4m3 -> f32
+            constexpr uint32_t idesc_wide = umma_idesc(0, 0, kBM, BN);  // e4m3 x e4m3 -> f32
+            constexpr uint32_t idesc_half = umma_idesc(0, 0, kBM, 128);
             const uint32_t me = warp - 1;
             uint32_t it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                const uint32_t idesc = u < wide_units ? idesc_wide : idesc_half;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     if ((it & 1) != me) continue;
                     const int s = it % S;
@@ -234,18 +265,19 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
         const int KBs = KB;
         uint32_t it = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-            const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
-            const int m = tc.m_blk * kBM + row_in_tile;
+        for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+            const Unit un = unit_of(u);
+            const bool active = half * 128 < un.ncols;       // the upper half sits out 128-wide units
+            const int m = un.m_blk * kBM + row_in_tile;
             const bool row_ok = m < M;
             const float* sa_row = sa + static_cast<int64_t>(row_ok ? m : 0) * KBs;
-            const float* sb_row = sb + static_cast<int64_t>(tc.n_blk * (BN / 128) + half) * KBs;
+            const float* sb_row = sb + static_cast<int64_t>(un.n_col0 / 128 + (active ? half : 0)) * KBs;
             float acc[128];                                  // this thread's 128 running sums
 #pragma unroll
             for (int j = 0; j < 128; ++j) acc[j] = 0.f;
-            ok = drain_tile<S, BN, false>(bar_empty, bar_tempty, it, t_lane, KB, sa_row, sb_row, acc, lane);
-            if (ok && row_ok)
-                store_row_bf16(out + static_cast<int64_t>(m) * ldo + tc.n_blk * BN + half * 128, acc);
+            ok = drain_tile<S, BN, false>(bar_empty, bar_tempty, it, t_lane, KB, sa_row, sb_row, acc, lane, active);
+            if (ok && row_ok && active)
+                store_row_bf16(out + static_cast<int64_t>(m) * ldo + un.n_col0 + half * 128, acc);
         }
     }
 
@@ -260,13 +292,15 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
 
 extern "C" __global__ void __launch_bounds__(Fp8Cfg<256>::kThreads, 1)
 tb200_k_gemm_fp8_bs_n256(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const float* sa, const float* sb, __nv_bfloat16* out, int M, int N, int K, int64_t ldo) {
-    gemm_fp8_body<256>(&tmap_a, &tmap_b, sa, sb, out, M, N, K, ldo);
+                         const __grid_constant__ CUtensorMap tmap_b128, const float* sa, const float* sb,
+                         __nv_bfloat16* out, int M, int N, int K, int64_t ldo, int wide_units) {
+    gemm_fp8_body<256>(&tmap_a, &tmap_b, &tmap_b128, sa, sb, out, M, N, K, ldo, wide_units);
 }
 extern "C" __global__ void __launch_bounds__(Fp8Cfg<128>::kThreads, 1)
 tb200_k_gemm_fp8_bs_n128(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const float* sa, const float* sb, __nv_bfloat16* out, int M, int N, int K, int64_t ldo) {
-    gemm_fp8_body<128>(&tmap_a, &tmap_b, sa, sb, out, M, N, K, ldo);
+                         const __grid_constant__ CUtensorMap tmap_b128, const float* sa, const float* sb,
+                         __nv_bfloat16* out, int M, int N, int K, int64_t ldo, int wide_units) {
+    gemm_fp8_body<128>(&tmap_a, &tmap_b, &tmap_b128, sa, sb, out, M, N, K, ldo, wide_units);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -449,15 +483,25 @@ static int launch_fp8(Kern kern, const void* a, const float* sa, const void* b, 
         TB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         attr_set[dev] = true;
     }
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tb128;
     int rc = encode_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, m, k, k, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TB200_OK) return rc;
     rc = encode_tmap_2d(&tb, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k, k, BN, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TB200_OK) return rc;
+    rc = encode_tmap_2d(&tb128, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k, k, 128, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TB200_OK) return rc;
     const int64_t tiles = ((m + kBM - 1) / kBM) * (n / BN);
     const int grid = static_cast<int>(tiles < num_sms() ? tiles : num_sms());
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(ta, tb, sa, sb, static_cast<__nv_bfloat16*>(out),
-                                                        static_cast<int>(m), static_cast<int>(n), static_cast<int>(k), ldo);
+    // Tail of the persistent schedule: if the last wave holds at most grid / 2 of the 256-wide tiles, cut each of
+    // them into two 128-wide units (4096^3: 512 tiles = 3 waves of 148 + 68 -> 136 half-units, 3.5 waves not 4).
+    int64_t wide_units = tiles;
+    if (BN == 256) {
+        const int64_t rest = tiles % grid;
+        if (rest > 0 && 2 * rest <= grid) wide_units = tiles - rest;
+    }
+    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(ta, tb, tb128, sa, sb, static_cast<__nv_bfloat16*>(out),
+                                                        static_cast<int>(m), static_cast<int>(n), static_cast<int>(k), ldo,
+                                                        static_cast<int>(wide_units));
     TB200_CUDA_TRY(cudaGetLastError());
     return TB200_OK;
 }
