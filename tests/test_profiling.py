@@ -18,3 +18,29 @@ def test_summary_picks_counters_and_stalls():
     assert e["stalls"] == "long_scoreboard 3.30"            # 0.01 is below the reporting threshold
     md = ncu_summary.to_markdown([e])
     assert md.startswith("### tb200_k_dequant_int8_rowwise_bf16") and "| dram__bytes_read.sum | 268.73 Mbyte |" in md
+
+
+def test_capture_command_follows_the_shared_gpu_rules(capsys):
+    from pathlib import Path
+    from tilebench_b200.profiling import ncu_one
+    cmd = ncu_one.ncu_command("gemm_fp8_blockscaled", {"S": 4096}, Path("out/x.ncu-rep"))
+    i = cmd.index("--clock-control")
+    assert cmd[i + 1] == "none"                                   # ncu must never lock the clocks
+    assert cmd[cmd.index("--profile-from-start") + 1] == "off"
+    assert cmd[cmd.index("-k") + 1] == "regex:tb200_k_gemm_fp8" and cmd[cmd.index("-c") + 1] == "2"
+    assert cmd[cmd.index("--set") + 1] == "full" and cmd[-6:-4] == ["-m", "tilebench_b200.profiling.harness"]
+    few = ncu_one.ncu_command("dequant_int8_channel", {}, Path("o.ncu-rep"), metrics=["gpu__time_duration.sum"])
+    assert "--set" not in few and few[few.index("--metrics") + 1] == "gpu__time_duration.sum"
+    assert ncu_one.main(["--operator", "matmul_int8", "--case", '{"K": 4096}', "--dry-run"]) == 0
+    plain, capture = capsys.readouterr().out.strip().split(" &&\n")
+    assert "ncu" not in plain.split()[0] and capture.startswith("ncu ") and capture.endswith(plain)   # plain run first, same command
+
+
+def test_capture_validation_names_foreign_kernels():
+    import pytest
+    from tilebench_b200.profiling import ncu_one
+    assert ncu_one.validate_capture(CSV, "dequant_int8_channel") == ["tb200_k_dequant_int8_rowwise_bf16"]
+    with pytest.raises(RuntimeError, match="not gemm_w4a16's"):
+        ncu_one.validate_capture(CSV, "gemm_w4a16")
+    with pytest.raises(RuntimeError, match="nothing was captured"):
+        ncu_one.validate_capture([["ID", "Kernel Name"], ["", ""]], "gemm_w4a16")
