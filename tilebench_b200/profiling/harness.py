@@ -49,7 +49,8 @@ def main() -> None:
     out = impl.run(*inputs)
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
-    print(json.dumps({"operator": args.operator, "case": case, "out_shape": list(out.shape)}))
+    outs = out if isinstance(out, (tuple, list)) else (out,)
+    print(json.dumps({"operator": args.operator, "case": case, "out_shapes": [list(o.shape) for o in outs]}))
 
 
 if __name__ == "__main__":
