@@ -92,8 +92,8 @@ int tb200_weight_dequant_block(const void* x, const void* s, void* y,
  * tilebench/benchmarks/operators/quantize_global/impl_torch.py:4-5).  One fp32 scale = amax / 448 per
  * [block_rows x 128] block (1 for an all-zero block), q = e4m3(x / scale) rounded to nearest even.
  *   x fp32 [rows, cols]   q e4m3 [rows, cols]   scales fp32 [rows / block_rows, cols / 128]
- * block_rows is 1 (activations) or 128 (weights); cols a multiple of 128.  Bit-exact against the same
- * formula in PyTorch.
+ * block_rows is 1 (activations) or 128 (weights); cols a multiple of 128 (rows too when block_rows is 128);
+ * x 32-byte and q 8-byte aligned (TB200_ERR_ALIGN otherwise).  Bit-exact against the same formula in PyTorch.
  */
 int tb200_quantize_fp8_block(const float* x, void* q, float* scales, int64_t rows, int64_t cols,
                              int block_rows, void* stream);
@@ -103,7 +103,8 @@ int tb200_quantize_fp8_block(const float* x, void* q, float* scales, int64_t row
  * reference, whose quantiser operator is a plain cast, tilebench/benchmarks/operators/quantize_global/impl_torch.py:4-5).
  *   x fp32 [n, k]  ->  wp uint8 [n, k/2] (low nibble = even k), scales fp16 [n, k/128]
  *   s = fp16(amax / 7) per group of 128 (1 where that rounds to zero), q = clamp(rint(x / s) + 8, 0, 15)
- * group must be 128 and zero_point 8.  Bit-exact against the same formula in PyTorch.
+ * group must be 128 and zero_point 8; x 32-byte and wp 4-byte aligned.  Bit-exact against the same formula
+ * in PyTorch.
  */
 int tb200_quantize_int4_group(const float* x, void* wp, void* scales, int64_t n, int64_t k, int64_t group,
                               int zero_point, void* stream);

@@ -14,9 +14,21 @@
 //   warps 1, 2   MMA issuers: warp 1 takes the first 32 packed rows of every stage, warp 2 the second
 //                32; per plane one tcgen05.mma kind::i8 (M = 128, N = BN, K = 32), each issuer into its
 //                own TMEM accumulator — integer addition is associative, the epilogue adds the two
-//   warps 4..11  unpack: shared-memory packed bytes -> four planes in the 128-byte-swizzled MN-major
-//                operand layout (two ping-pong buffers, one per issuer)
-//   warps 12..15 epilogue: tcgen05.ld both accumulators, add, store int32 rows
+//   warps 4..11  unpack: shared-memory packed bytes -> planes in the 128-byte-swizzled MN-major operand
+//                layout.  Four groups of two warps, each with its own two-plane buffer: group g turns
+//                the packed rows of sub-step g / 2 into planes 2 (g % 2) and 2 (g % 2) + 1 of every
+//                stage.  One pass of a group is a latency chain (wait, load, unpack, store, proxy fence,
+//                arrive, two MMAs, commit, wake-up) much longer than its arithmetic, so four chains run
+//                side by side instead of eight warps walking one chain together
+//   warps 12..15 row sums of a during the main loop, then the epilogue: tcgen05.ld both accumulators,
+//                add, subtract the row sum, store int32 rows
+//
+// The "- 1" of the decode is taken out of the inner loop: sum_k a * (f - 1) = sum_k a * f - sum_k a.  The
+// unpack warps, whose instruction chain paces the kernel, only shift and mask (the planes hold the raw
+// fields 0..3, fed to the tensor cores as UNSIGNED 8-bit against the signed a), and the four epilogue
+// warps, otherwise idle until the accumulators complete, add up their own row of every a slice from
+// shared memory (dp4a against ones) and subtract that once per tile.  All of it is int32 arithmetic, so
+// the result is the same number bit for bit.
 // Every mbarrier wait is bounded and reports through g_status.
 #include "common.cuh"
 
@@ -34,12 +46,15 @@ template <int BN> struct I8Cfg {
     static constexpr int kPackedBytes = kI8StageRows * BN;
     static constexpr int kStageBytes = kI8ABytes + kPackedBytes;
     static constexpr int kPlaneBytes = kI8SubRows * BN;         // one unpacked plane of one sub-step
-    static constexpr int kUBufBytes = 4 * kPlaneBytes;
+    static constexpr int kGroups = 4;                           // unpack groups = unpacked buffers
+    static constexpr int kGroupWarps = 2;
+    static constexpr int kGroupBufBytes = 2 * kPlaneBytes;      // two planes of one sub-step
     static constexpr int kThreads = 512;
     static constexpr int kConvertWarps = 8;
     static constexpr int kTmemCols = 2 * BN;                    // one accumulator per issuer
     static constexpr int kBarBytes = 256;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 2 * kUBufBytes + kBarBytes + 1024;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kGroups * kGroupBufBytes + kBarBytes + 1024;
+    static_assert(kGroups * kGroupWarps == kConvertWarps, "unpack warps");
 };
 
 // K-major operand stored with the 64-byte swizzle (rows of 64 bytes, 8-row groups 512 bytes apart)
@@ -64,10 +79,10 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
     d |= static_cast<uint64_t>(2) << 61;
     return d;
 }
-// kind::i8 instruction descriptor: D = s32 (2 at [4,6)), A and B signed 8-bit (1 at [7,10) and [10,13)),
-// A K-major, B MN-major (bit 16), N >> 3 at [17,23), M >> 4 at [24,29).
+// kind::i8 instruction descriptor: D = s32 (2 at [4,6)), A signed 8-bit (1 at [7,10)), B unsigned 8-bit
+// (0 at [10,13)), A K-major, B MN-major (bit 16), N >> 3 at [17,23), M >> 4 at [24,29).
 __host__ __device__ constexpr uint32_t umma_idesc_i8(uint32_t m, uint32_t n) {
-    return (2u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+    return (2u << 4) | (1u << 7) | (0u << 10) | (1u << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 __device__ __forceinline__ void umma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                            uint32_t accumulate) {
@@ -79,11 +94,17 @@ __device__ __forceinline__ void umma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uin
         : "memory");
 }
 
-// four packed bytes -> field i of each, minus one, as four int8 (0..3 -> -1..2).  Setting bit 7 of
-// every byte before the subtraction keeps the borrow inside the byte.
+// four packed bytes -> field i of each as four unsigned bytes 0..3 (the "- 1" is applied per row in the
+// epilogue)
 __device__ __forceinline__ uint32_t unpack_field(uint32_t w, int i) {
-    const uint32_t x = ((w >> (2 * i)) & 0x03030303u) | 0x80808080u;
-    return (x - 0x01010101u) ^ 0x80808080u;
+    return (w >> (2 * i)) & 0x03030303u;
+}
+// sum of the sixteen signed bytes of v, added to acc
+__device__ __forceinline__ int32_t add_bytes16(const uint4& v, int32_t acc) {
+    acc = __dp4a(static_cast<int>(v.x), 0x01010101, acc);
+    acc = __dp4a(static_cast<int>(v.y), 0x01010101, acc);
+    acc = __dp4a(static_cast<int>(v.z), 0x01010101, acc);
+    return __dp4a(static_cast<int>(v.w), 0x01010101, acc);
 }
 
 }  // namespace
@@ -98,12 +119,12 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
     constexpr int S = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* ubuf = smem + S * Cfg::kStageBytes;                  // [2][4 planes][32 x BN]
-    uint64_t* bar_full = reinterpret_cast<uint64_t*>(ubuf + 2 * Cfg::kUBufBytes);
-    uint64_t* bar_empty = bar_full + S;       // stage consumed: 2 issuer commits + 8 unpack warps
-    uint64_t* bar_ufull = bar_empty + S;      // [2] unpacked buffer written (8 unpack warps)
-    uint64_t* bar_ufree = bar_ufull + 2;      // [2] unpacked buffer read by its issuer's MMAs
-    uint64_t* bar_afull = bar_ufree + 2;      // both accumulators complete (2 issuer commits)
+    uint8_t* ubuf = smem + S * Cfg::kStageBytes;                  // [4 groups][2 planes][32 x BN]
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(ubuf + Cfg::kGroups * Cfg::kGroupBufBytes);
+    uint64_t* bar_empty = bar_full + S;       // stage consumed: 2 issuer commits + 8 unpack warps + 4 row-sum warps
+    uint64_t* bar_ufull = bar_empty + S;      // [4] group buffer written (the group's 2 warps)
+    uint64_t* bar_ufree = bar_ufull + Cfg::kGroups;   // [4] group buffer read by its issuer's MMAs
+    uint64_t* bar_afull = bar_ufree + Cfg::kGroups;   // both accumulators complete (2 issuer commits)
     uint64_t* bar_aempty = bar_afull + 1;     // both accumulators drained (4 epilogue warps)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_aempty + 1);
 
@@ -118,10 +139,10 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(&bar_full[s], 1);
-            mbar_init(&bar_empty[s], 2 + Cfg::kConvertWarps);
+            mbar_init(&bar_empty[s], 2 + Cfg::kConvertWarps + 4);
         }
-        for (int u = 0; u < 2; ++u) {
-            mbar_init(&bar_ufull[u], Cfg::kConvertWarps);
+        for (int u = 0; u < Cfg::kGroups; ++u) {
+            mbar_init(&bar_ufull[u], Cfg::kGroupWarps);
             mbar_init(&bar_ufree[u], 1);
         }
         mbar_init(bar_afull, 2);
@@ -172,9 +193,9 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
         // ---------------- MMA issuers ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_i8(kI8BM, BN);
-            const uint32_t me = warp - 1;                         // sub-step of every stage, unpacked buffer, accumulator
+            const uint32_t me = warp - 1;                         // sub-step of every stage, accumulator; groups 2 me, 2 me + 1
             const uint32_t d_tmem = tmem_base + me * BN;
-            const uint32_t u_addr = smem_u32(ubuf + me * Cfg::kUBufBytes);
+            const uint32_t u_addr = smem_u32(ubuf + 2 * me * Cfg::kGroupBufBytes);
             uint32_t n = 0;                                       // stages seen so far (= own sub-steps)
             uint32_t tile_cnt = 0;
             bool ok = true;
@@ -184,16 +205,20 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
                 for (int ks = 0; ks < KS; ++ks, ++n) {
                     const int s = n % S;
                     if (!mbar_wait(&bar_full[s], (n / S) & 1, ST_WAIT_SMEM_FULL, ks)) { ok = false; break; }
-                    if (!mbar_wait(&bar_ufull[me], n & 1, ST_WAIT_OPERAND, ks)) { ok = false; break; }
-                    tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes) + me * kI8SubRows;   // +32 B along K
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        umma_i8_ss(d_tmem, umma_desc_k_sw64(a_addr + i * kI8APlaneBytes),
-                                   umma_desc_mn_sw128(u_addr + i * Cfg::kPlaneBytes, kI8SubRows * 128), idesc,
-                                   (ks > 0 || i > 0) ? 1u : 0u);
+                    for (int h = 0; h < 2; ++h) {                 // the two groups of this sub-step
+                        if (!mbar_wait(&bar_ufull[2 * me + h], n & 1, ST_WAIT_OPERAND, ks)) { ok = false; break; }
+                        tc_fence_after();
+#pragma unroll
+                        for (int i = 2 * h; i < 2 * h + 2; ++i) {
+                            umma_i8_ss(d_tmem, umma_desc_k_sw64(a_addr + i * kI8APlaneBytes),
+                                       umma_desc_mn_sw128(u_addr + i * Cfg::kPlaneBytes, kI8SubRows * 128), idesc,
+                                       (ks > 0 || i > 0) ? 1u : 0u);
+                        }
+                        tc_commit(&bar_ufree[2 * me + h]);
                     }
-                    tc_commit(&bar_ufree[me]);
+                    if (!ok) break;
                     tc_commit(&bar_empty[s]);
                 }
                 if (ok) tc_commit(bar_afull);
@@ -203,43 +228,48 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
         // ---------------- unpack warps ----------------
         constexpr int kChunksPerRow = BN / 16;
         constexpr int kChunks = kI8SubRows * kChunksPerRow;       // 16-byte chunks per sub-step
-        constexpr int kPerThread = kChunks / (32 * Cfg::kConvertWarps);
+        constexpr int kGroupThreads = 32 * Cfg::kGroupWarps;
+        constexpr int kPerThread = kChunks / kGroupThreads;
         static_assert(kPerThread >= 1, "unpack mapping");
-        const int ct = threadIdx.x - 4 * 32;
+        const int g = (warp - 4) / Cfg::kGroupWarps;              // group = buffer
+        const int j = g >> 1, h = g & 1;                          // sub-step, plane pair
+        const int gt = threadIdx.x - (4 + g * Cfg::kGroupWarps) * 32;
+        uint8_t* dst = ubuf + g * Cfg::kGroupBufBytes;
         uint32_t n = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
             for (int ks = 0; ks < KS && ok; ++ks, ++n) {
                 const int s = n % S;
                 if (!mbar_wait(&bar_full[s], (n / S) & 1, ST_WAIT_SMEM_FULL, ks)) { ok = false; break; }
-                const uint8_t* packed = smem + s * Cfg::kStageBytes + kI8ABytes;
+                const uint8_t* packed = smem + s * Cfg::kStageBytes + kI8ABytes + j * kI8SubRows * BN;
+                uint4 w[kPerThread];
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {                     // the two sub-steps -> the two unpacked buffers
-                    if (!mbar_wait(&bar_ufree[j], (n & 1) ^ 1, ST_WAIT_SMEM_EMPTY, -ks - 1)) { ok = false; break; }
-                    uint8_t* dst = ubuf + j * Cfg::kUBufBytes;
-#pragma unroll
-                    for (int c = 0; c < kPerThread; ++c) {
-                        const int chunk = ct + c * 32 * Cfg::kConvertWarps;
-                        const int row = chunk / kChunksPerRow, col16 = chunk % kChunksPerRow;
-                        const uint4 w = *reinterpret_cast<const uint4*>(packed + (j * kI8SubRows + row) * BN + col16 * 16);
-                        const int off = (col16 >> 3) * (kI8SubRows * 128) + row * 128 + (((col16 & 7) ^ (row & 7)) << 4);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            uint4 o;
-                            o.x = unpack_field(w.x, i);
-                            o.y = unpack_field(w.y, i);
-                            o.z = unpack_field(w.z, i);
-                            o.w = unpack_field(w.w, i);
-                            *reinterpret_cast<uint4*>(dst + i * Cfg::kPlaneBytes + off) = o;
-                        }
-                    }
-                    fence_async_smem();                           // generic-proxy writes -> visible to the MMA's reads
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&bar_ufull[j]);
+                for (int c = 0; c < kPerThread; ++c) {
+                    const int chunk = gt + c * kGroupThreads;
+                    w[c] = *reinterpret_cast<const uint4*>(packed + (chunk / kChunksPerRow) * BN + (chunk % kChunksPerRow) * 16);
                 }
-                if (ok) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&bar_empty[s]);    // packed bytes of this stage are consumed
+                if (!mbar_wait(&bar_ufree[g], (n & 1) ^ 1, ST_WAIT_SMEM_EMPTY, -ks - 1)) { ok = false; break; }
+#pragma unroll
+                for (int c = 0; c < kPerThread; ++c) {
+                    const int chunk = gt + c * kGroupThreads;
+                    const int row = chunk / kChunksPerRow, col16 = chunk % kChunksPerRow;
+                    const int off = (col16 >> 3) * (kI8SubRows * 128) + row * 128 + (((col16 & 7) ^ (row & 7)) << 4);
+#pragma unroll
+                    for (int p = 0; p < 2; ++p) {
+                        const int i = 2 * h + p;
+                        uint4 o;
+                        o.x = unpack_field(w[c].x, i);
+                        o.y = unpack_field(w[c].y, i);
+                        o.z = unpack_field(w[c].z, i);
+                        o.w = unpack_field(w[c].w, i);
+                        *reinterpret_cast<uint4*>(dst + p * Cfg::kPlaneBytes + off) = o;
+                    }
+                }
+                fence_async_smem();                               // generic-proxy writes -> visible to the MMA's reads
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&bar_ufull[g]);
+                    mbar_arrive(&bar_empty[s]);                   // this warp's packed bytes are in registers / consumed
                 }
             }
         }
@@ -247,11 +277,36 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
         // ---------------- epilogue ----------------
         const int ew = warp - 12;                                  // == warp % 4: TMEM lanes 32 * ew ..
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(ew * 32) << 16);
-        uint32_t tile_cnt = 0;
+        // this thread's row of an a slice: 64 bytes at row * 64, its four 16-byte chunks permuted by the
+        // 64-byte swizzle (chunk ^ bits [1,3) of the row).  A sum visits them in any order; reading chunk
+        // (c ^ that key) makes the eight lanes of a quarter-warp hit eight different 16-byte bank groups.
+        const int row = ew * 32 + lane;
+        const uint32_t row_off = row * 64, key = (row >> 1) & 3;
+        uint32_t tile_cnt = 0, n = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++tile_cnt) {
             const int m_blk = t % tiles_m, n_blk = t / tiles_m;
-            const int m = m_blk * kI8BM + ew * 32 + lane;
+            const int m = m_blk * kI8BM + row;
+            int32_t rs0 = 0, rs1 = 0;                              // sum_k a[m, k] (rows past M are zero-filled by TMA)
+            for (int ks = 0; ks < KS; ++ks, ++n) {
+                const int s = n % S;
+                if (!mbar_wait(&bar_full[s], (n / S) & 1, ST_WAIT_SMEM_FULL, ks)) { ok = false; break; }
+                const uint8_t* a_row = smem + s * Cfg::kStageBytes + row_off;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                    for (int c = 0; c < 4; c += 2) {
+                        const uint4 u = *reinterpret_cast<const uint4*>(a_row + i * kI8APlaneBytes + (((c + 0) ^ key) << 4));
+                        const uint4 v = *reinterpret_cast<const uint4*>(a_row + i * kI8APlaneBytes + (((c + 1) ^ key) << 4));
+                        rs0 = add_bytes16(u, rs0);
+                        rs1 = add_bytes16(v, rs1);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_empty[s]);        // this warp's rows of the a slices are read
+            }
+            if (!ok) break;
+            const uint32_t rs = static_cast<uint32_t>(rs0 + rs1);
             if (!mbar_wait(bar_afull, tile_cnt & 1, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
             tc_fence_after();
             int32_t* dst = out + static_cast<int64_t>(m < M ? m : 0) * ldo + n_blk * BN;
@@ -270,10 +325,10 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
                         int4 o;
-                        o.x = static_cast<int32_t>(v0[4 * q + 0] + v1[4 * q + 0]);
-                        o.y = static_cast<int32_t>(v0[4 * q + 1] + v1[4 * q + 1]);
-                        o.z = static_cast<int32_t>(v0[4 * q + 2] + v1[4 * q + 2]);
-                        o.w = static_cast<int32_t>(v0[4 * q + 3] + v1[4 * q + 3]);
+                        o.x = static_cast<int32_t>(v0[4 * q + 0] + v1[4 * q + 0] - rs);
+                        o.y = static_cast<int32_t>(v0[4 * q + 1] + v1[4 * q + 1] - rs);
+                        o.z = static_cast<int32_t>(v0[4 * q + 2] + v1[4 * q + 2] - rs);
+                        o.w = static_cast<int32_t>(v0[4 * q + 3] + v1[4 * q + 3] - rs);
                         *reinterpret_cast<int4*>(dst + c * 32 + 4 * q) = o;
                     }
                 }
