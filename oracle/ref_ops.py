@@ -10,15 +10,25 @@ round-to-nearest-even from fp32, so the integer -> float paths are bit-exact sta
   * bf16  as uint16 bit patterns via `f32_to_bf16_bits`
   * e4m3  decoded from the format definition by `e4m3_table`
 
-Pinning:
-  * dequantize_rowwise, weight_dequant and the fp16/fp32 matmul are checked against outputs of the
-    reference's own impl_torch.run (fixtures in tests/golden/reference_ops.npz, generated by
-    tests/golden/make_golden.py from a reference checkout) and against the worked examples in
+Pinning — every function is checked against outputs of REFERENCE code, generated from a reference
+checkout by tests/golden/make_golden.py and committed as fixtures:
+  * dequantize_rowwise, weight_dequant, the 2-bit matmul_int8 and the fp16/fp32 matmul: outputs of the
+    reference's own impl_torch.run (tests/golden/reference_ops.npz), plus the worked examples in
     tilebench/problems/*_current.md.
-  * dequant_int4_group, dequant_int8_channel, gemm_w4a16 and gemm_fp8_blockscaled have no
-    counterpart in the reference (it has no int4, W4A16 or block-scaled FP8 operator): PARITY
-    UNPINNED by the reference for these four.  They are pinned by hand-computable known-answer
-    tests (all 16 nibbles, all 256 int8 / e4m3 codes, identity scales, one-hot activations).
+  * dequant_int4_group, dequant_int8_channel, gemm_w4a16, gemm_fp8_blockscaled, quantize_int4_group have
+    no operator of their own in the reference (it has no int4, W4A16 or block-scaled FP8 operator), so
+    their fixtures (tests/golden/baseline_configs.npz) are computed THROUGH the reference operators that
+    carry their arithmetic: weight_dequant.impl_torch.run with TILE_SIZE = 1 is the elementwise fp32
+    multiply of both dequant formulas (and, with TILE_SIZE = 128, the block scaling of the FP8 weights),
+    matmul_fp32_fp16_fp8.impl_torch.run on fp32 tensors is the "fp32 matmul of the dequantised operands"
+    the GEMM configurations name, quantize_global.impl_torch.run is the fp16 cast of the quantiser's
+    scale.  Around them only nibble extraction, broadcasting and the final cast to the output type are
+    added.  The dequant fixtures are matched bit for bit; the GEMM fixtures within the operator's
+    tolerance (two fp32 GEMMs with different summation orders) with over 98 % of the outputs identical.
+  * Beside the fixtures: hand-computable known answers (all 16 nibbles, all 256 int8 / e4m3 codes,
+    identity scales, one-hot activations).
+  * The e4m3 row of matmul_plain follows torch._scaled_mm, which does not run on CPU: no reference
+    fixture; its pieces (decode table, encoder) are checked against PyTorch's casts on dense sweeps.
 """
 from __future__ import annotations
 
@@ -101,7 +111,8 @@ def dequant_int4_group(wp, scales_f16, group: int = 128, zp: int = 8) -> np.ndar
     (tilebench/llm/v2/contracts/data/weight_dequant/contract.md:60-67)."""
     q = unpack_int4(wp)
     s = np.repeat(np.asarray(scales_f16, dtype=np.float16).astype(np.float32), group, axis=1)
-    return ((q - zp).astype(np.float32) * s).astype(np.float16)
+    with np.errstate(over="ignore"):                   # products beyond 65504 round to +-inf, as IEEE says
+        return ((q - zp).astype(np.float32) * s).astype(np.float16)
 
 
 def quantize_int4_group(x_f32, group: int = 128, zp: int = 8):

@@ -21,6 +21,14 @@ def golden():
 
 
 @pytest.fixture(scope="session")
+def golden_cfg():
+    """Fixtures for the operators the reference lacks, computed through the reference's own multiply and
+    fp32 matmul operators (tests/golden/make_golden.py, second half)."""
+    import numpy as np
+    return np.load(ROOT / "tests" / "golden" / "baseline_configs.npz")
+
+
+@pytest.fixture(scope="session")
 def cuda_device():
     import torch
     if not torch.cuda.is_available():

@@ -109,6 +109,33 @@ def test_int8_channel_full_size_chunked_check(cuda_device):
     assert torch.equal(out2.float(), out.float() * 2)
 
 
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_int4_group_matches_reference_fixture(cuda_device, golden_cfg, tag):
+    # expected output computed by the reference's own multiply operator (tests/golden/make_golden.py)
+    ext = native.load()
+    group, zp = (int(v) for v in golden_cfg[f"i4_{tag}_gz"])
+    wp = torch.from_numpy(golden_cfg[f"i4_{tag}_wp"]).to(cuda_device)
+    sc = torch.from_numpy(golden_cfg[f"i4_{tag}_s"]).to(cuda_device)
+    out = torch.empty(wp.shape[0], wp.shape[1] * 2, dtype=torch.float16, device=cuda_device)
+    ext.dequant_int4_group(wp, sc, out, group, zp)
+    assert np.array_equal(bits16(out), golden_cfg[f"i4_{tag}_out"].view(np.uint16))
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
+def test_int8_channel_matches_reference_fixture(cuda_device, golden_cfg, tag):
+    from tilebench_b200.benchmarks.operators.dequant_int8_channel import impl_cuda
+    out = impl_cuda.run(torch.from_numpy(golden_cfg[f"i8_{tag}_w"]).to(cuda_device),
+                        torch.from_numpy(golden_cfg[f"i8_{tag}_scale"]).to(cuda_device))
+    assert np.array_equal(bits16(out), golden_cfg[f"i8_{tag}_out"])
+
+
+def test_int4_quantiser_matches_reference_fixture(cuda_device, golden_cfg):
+    from tilebench_b200.benchmarks.operators.quantize_int4_group import impl_cuda
+    wp, s = impl_cuda.run(torch.from_numpy(golden_cfg["q4_x"]).to(cuda_device), 128, 8)
+    assert np.array_equal(wp.cpu().numpy(), golden_cfg["q4_wp"])
+    assert np.array_equal(bits16(s), golden_cfg["q4_s"].view(np.uint16))
+
+
 @pytest.mark.parametrize("tag", ["a", "b", "c"])
 def test_dequantize_rowwise_matches_reference_fixture(cuda_device, golden, tag):
     from tilebench_b200.benchmarks.operators.dequantize_rowwise import impl_cuda

@@ -56,6 +56,20 @@ def test_fp8_small_integers_exact(cuda_device):
     assert np.array_equal(got, want)
 
 
+def test_fp8_matches_reference_fixture(cuda_device, golden_cfg):
+    """Expected output = the reference's fp32 matmul operator on operands dequantised by the reference's
+    block-scale multiply (tests/golden/make_golden.py); ragged m, an all-zero block in each operand,
+    +-448 codes and a subnormal fp32 scale."""
+    from tilebench_b200.benchmarks.operators.gemm_fp8_blockscaled import impl_cuda
+    aq = torch.from_numpy(golden_cfg["f8_aq"]).view(torch.float8_e4m3fn).to(cuda_device)
+    bq = torch.from_numpy(golden_cfg["f8_bq"]).view(torch.float8_e4m3fn).to(cuda_device)
+    native.clear_device_status()
+    out = impl_cuda.run(aq, torch.from_numpy(golden_cfg["f8_sa"]).to(cuda_device), bq, torch.from_numpy(golden_cfg["f8_sb"]).to(cuda_device))
+    torch.cuda.synchronize()
+    status_clean()
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref_ops.bf16_bits_to_f32(golden_cfg["f8_out"]), **BF16_TOL)
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (1024, 1024, 1024), (200, 256, 384), (1, 128, 128)])
 def test_fp8_matches_oracle_n128_tiles(cuda_device, M, N, K):
     got, want = fp8_case(M, N, K, seed=M + N + K, device=cuda_device)
@@ -107,6 +121,20 @@ def test_fp8_rejects_bad_shapes(cuda_device):
 
 
 # ---------------------------------------------------------------- W4A16
+
+@pytest.mark.parametrize("m", [1, 16, 33, 130])
+def test_w4a16_matches_reference_fixture(cuda_device, golden_cfg, m):
+    """Expected output = the reference's fp32 matmul operator on the activations and the weights dequantised
+    by the reference's multiply (tests/golden/make_golden.py); one height per kernel family."""
+    from tilebench_b200.benchmarks.operators.gemm_w4a16 import impl_cuda
+    group, zp = (int(v) for v in golden_cfg["w4_gz"])
+    native.clear_device_status()
+    out = impl_cuda.run(torch.from_numpy(golden_cfg[f"w4_m{m}_a"]).to(cuda_device), torch.from_numpy(golden_cfg["w4_wp"]).to(cuda_device),
+                        torch.from_numpy(golden_cfg["w4_s"]).to(cuda_device), group, zp)
+    torch.cuda.synchronize()
+    status_clean()
+    np.testing.assert_allclose(out.float().cpu().numpy(), golden_cfg[f"w4_m{m}_out"].astype(np.float32), **FP16_TOL)
+
 
 def w4_case(M, N, K, seed, device, group=128):
     from tilebench_b200.benchmarks.operators.gemm_w4a16 import impl_cuda

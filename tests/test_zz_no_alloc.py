@@ -4,13 +4,13 @@ Some users of the library cannot hand it a workspace: they run where device allo
 available to them (all memory already belongs to the host application's pool, or allocation calls
 are forbidden at that point).  For them the split-K partial sums live in a fixed array inside the
 library.  This test calls both entry points through the C ABI on the same inputs, twice in a row
-with different data, and expects the same fp16 result within the GEMM tolerance used elsewhere
-(atol 1e-3 / rtol 1e-3) — the second call proves that whatever the first left in the shared array
-does not leak into later results.  The file sorts last so a `-x` run reaches it after everything else.
+with different data.  Both run the same kernels with the same split of K and add the partial sums
+in the same order, so the fp16 results must be equal bit for bit (which is inside the GEMM
+tolerance used elsewhere, atol 1e-3 / rtol 1e-3) — the second call proves that whatever the first
+left in the shared array does not leak into later results.  The file sorts last so a `-x` run reaches it after everything else.
 """
 import ctypes
 
-import numpy as np
 import pytest
 import torch
 
@@ -18,8 +18,6 @@ from tilebench_b200 import native
 from tilebench_b200.data import tensors
 
 pytestmark = pytest.mark.gpu
-
-FP16_TOL = dict(atol=1e-3, rtol=1e-3)
 
 
 def vp(t):
@@ -51,7 +49,8 @@ def test_static_scratch_matches_workspace_entry_point_twice(cuda_device):
     for seed, m in ((101, 24), (202, 17)):
         need, got, ref = run_pair(lib, cuda_device, m, 14336, 4096, seed)
         assert 0 < need <= 16 << 20
-        np.testing.assert_allclose(got.float().cpu().numpy(), ref.float().cpu().numpy(), **FP16_TOL)
+        assert not torch.isnan(got).any()
+        assert torch.equal(got, ref)
     assert native.device_status()[0] == 0
 
 
@@ -59,7 +58,7 @@ def test_static_entry_point_without_scratch_and_over_the_limit(cuda_device):
     lib = native.capi()
     need, got, ref = run_pair(lib, cuda_device, 256, 512, 1024, seed=303)      # large m: no scratch at all
     assert need == 0
-    np.testing.assert_allclose(got.float().cpu().numpy(), ref.float().cpu().numpy(), **FP16_TOL)
+    assert torch.equal(got, ref)
     # a shape whose partial sums do not fit is refused with a message, not run
     m, k = 64, 4096
     n = next((c for c in (14336, 28672, 57344, 8192) if lib.tb200_gemm_w4a16_workspace_bytes(m, c, k) > 16 << 20), None)
