@@ -93,7 +93,8 @@ int tb200_weight_dequant_block(const void* x, const void* s, void* y,
  * [block_rows x 128] block (1 for an all-zero block), q = e4m3(x / scale) rounded to nearest even.
  *   x fp32 [rows, cols]   q e4m3 [rows, cols]   scales fp32 [rows / block_rows, cols / 128]
  * block_rows is 1 (activations) or 128 (weights); cols a multiple of 128 (rows too when block_rows is 128);
- * x 32-byte and q 8-byte aligned (TB200_ERR_ALIGN otherwise).  Bit-exact against the same formula in PyTorch.
+ * x 32-byte and q 8-byte aligned (TB200_ERR_ALIGN otherwise).  Bit-exact against the same formula in PyTorch
+ * for finite inputs; a NaN element is ignored by the block's amax (PyTorch's amax would propagate it).
  */
 int tb200_quantize_fp8_block(const float* x, void* q, float* scales, int64_t rows, int64_t cols,
                              int block_rows, void* stream);
@@ -104,7 +105,8 @@ int tb200_quantize_fp8_block(const float* x, void* q, float* scales, int64_t row
  *   x fp32 [n, k]  ->  wp uint8 [n, k/2] (low nibble = even k), scales fp16 [n, k/128]
  *   s = fp16(amax / 7) per group of 128 (1 where that rounds to zero), q = clamp(rint(x / s) + 8, 0, 15)
  * group must be 128 and zero_point 8; x 32-byte and wp 4-byte aligned.  Bit-exact against the same formula
- * in PyTorch.
+ * in PyTorch for finite inputs whose group amax / 7 stays inside the fp16 range (65504); NaN elements are
+ * ignored by the amax, and a larger amax makes the fp16 scale infinite (every code of the group becomes 8).
  */
 int tb200_quantize_int4_group(const float* x, void* wp, void* scales, int64_t n, int64_t k, int64_t group,
                               int zero_point, void* stream);
@@ -119,7 +121,7 @@ int tb200_quantize_int4_group(const float* x, void* wp, void* scales, int64_t n,
  *   a   e4m3 [m, k]   sa fp32 [m, k/128]          (one scale per 1x128 block of A)
  *   b   e4m3 [n, k]   sb fp32 [n/128, k/128]      (one scale per 128x128 block of B)
  *   out bf16 [m, ldo] = bf16( sum_kb sa[i,kb] * sb[j/128,kb] * dot(a[i,kb*128:+128], b[j,kb*128:+128]) )
- * fp32 accumulation.  m, n multiples of 128, k a multiple of 128; a, b, out 16-byte aligned.
+ * fp32 accumulation.  Any m >= 1; n and k multiples of 128; a, b, out 16-byte aligned.
  */
 int tb200_gemm_fp8_blockscaled(const void* a, const float* sa, const void* b, const float* sb,
                                void* out, int64_t m, int64_t n, int64_t k, int64_t ldo,
@@ -157,12 +159,14 @@ int tb200_matmul_plain(const void* a, const void* b, void* out, int64_t m, int64
  * W4A16 dequant-fused GEMM (new operator `gemm_w4a16`; structural template: the packed-weight
  * GEMM tilebench/benchmarks/operators/matmul_int8/impl_torch.py:4-19).
  *   a       fp16  [m, k]
- *   wp      uint8 [n, k/2], scales fp16 [n, k/group]   as in tb200_dequant_int4_group (group = 128)
+ *   wp      uint8 [n, k/2], scales fp16 [n, k/group]   as in tb200_dequant_int4_group; group a multiple of 64
+ *           that divides k (128 in the benchmark configurations)
  *   out     fp16  [m, ldo]; this call writes columns [col_offset, col_offset + n) — an N-partitioned
  *           rank passes its slice of wp/scales and the offset of its slice in the full output
  *   out[i, col_offset + j] = fp16( sum_k float(a[i,k]) * float(fp16((q[j,k]-zp) * scales[j,k/group])) )
- *   workspace  fp32 scratch for the split-K variant chosen for small m; size from
- *              tb200_gemm_w4a16_workspace_bytes(); may be NULL when that returns 0
+ *   workspace  fp32 scratch for the split-K variant chosen for 17 <= m <= 64; size from
+ *              tb200_gemm_w4a16_workspace_bytes(), which holds for every valid group; may be NULL when
+ *              that returns 0 (always the case for m <= 16 and m > 64)
  * n a multiple of 128, k a multiple of 128.
  */
 size_t tb200_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k);
@@ -210,6 +214,20 @@ int    tb200_gemm_w4a16_static(const void* a, const void* wp, const void* scales
                                int64_t m, int64_t n, int64_t k, int64_t group, int zero_point,
                                int64_t ldo, int64_t col_offset, void* stream);
 
+/*
+ * Exchange step of the N-partitioned GEMM without the GEMM: pushes this rank's column slice into every rank's
+ * full result (the reference has no multi-GPU path; this is the unfused counterpart of tb200_gemm_w4a16_gather).
+ *   local     [m, ld_local] elements of elem_bytes: this rank's slice, columns [0, n_local)
+ *   out_ptrs  HOST array of `world` device pointers: rank r's full result [m, ldo], peer-mapped into this
+ *             process for r != rank; the slice lands in columns [rank * n_local, (rank + 1) * n_local) of each.
+ *             When out_ptrs[rank] already holds the slice at that place (local points there) it is not copied.
+ * One streaming kernel: loads from this GPU, 128-bit stores to each destination; no staging buffer, no
+ * interleave pass, no loads from another GPU.  Row slices, pitches and pointers must be multiples of 16 bytes.
+ * Callers put a cross-rank barrier between this call and any read of a gathered buffer.
+ */
+int tb200_allgather_cols(const void* local, int64_t ld_local, void* const* out_ptrs, int world, int rank,
+                         int64_t m, int64_t n_local, int64_t elem_bytes, int64_t ldo, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Device status word.  Every wait inside the GEMM kernels (mbarrier, TMEM hand-off) is bounded;
  * a wait that runs out records a code here and the kernel drains and returns instead of hanging.
@@ -217,6 +235,13 @@ int    tb200_gemm_w4a16_static(const void* a, const void* wp, const void* scales
  * ------------------------------------------------------------------------------------------- */
 int tb200_device_status(int* code, int* detail);   /* code 0 = clean */
 int tb200_clear_device_status(void);
+/*
+ * Self-test of that mechanism: launches one warp that waits, with a limit of `limit_cycles` SM clock cycles
+ * (1 .. 2^28), on a barrier nothing ever arrives on.  The wait runs out, the kernel records status code 6 and
+ * returns normally; tb200_device_status() then reports (6, limit) until tb200_clear_device_status().  The
+ * context stays usable.  No counterpart in the reference.
+ */
+int tb200_selftest_bounded_wait(int64_t limit_cycles, void* stream);
 
 #ifdef __cplusplus
 }

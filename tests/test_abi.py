@@ -41,6 +41,11 @@ def test_version_and_error_text_without_gpu(built):
     rc = built.tb200_gemm_fp8_blockscaled(None, None, None, None, None, 128, 128, 128, 128, None)
     assert rc == 1
     assert built.tb200_gemm_w4a16_workspace_bytes(4096, 14336, 4096) == 0      # large m: no split-K scratch
+    assert built.tb200_gemm_w4a16_workspace_bytes(8, 14336, 4096) == 0         # decode-sized m: never, whatever the group
+    # the exchange step and the wait self-test validate on the host too
+    assert built.tb200_allgather_cols(None, 8, None, 2, 0, 4, 8, 2, 16, None) == 1
+    assert built.tb200_selftest_bounded_wait(0, None) == 1 and b"limit" in built.tb200_last_error()
+    assert built.tb200_selftest_bounded_wait(1 << 40, None) == 1
 
 
 def test_extension_imports_and_mirrors_the_abi(built):

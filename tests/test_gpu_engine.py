@@ -52,7 +52,7 @@ def test_config3_fp8_blockscaled_gemm_all_sizes(cuda_device):
 
 def test_config4_npart_single_gpu_cases(cuda_device):
     # WORLD=1 with and without the (trivial) gather; the multi-rank cases run under torch.distributed
-    check(run_benchmark_suite("gemm_w4a16_npart", {**FAST, "case_indices": [0, 1, 2]}, ["cuda"]), 3, graph=False)
+    check(run_benchmark_suite("gemm_w4a16_npart", {**FAST, "case_indices": [0, 1, 2, 3]}, ["cuda"]), 4, graph=False)
 
 
 def test_config4_npart_single_gpu_under_graph_capture(cuda_device):

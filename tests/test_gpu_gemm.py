@@ -173,6 +173,18 @@ def test_w4a16_matches_oracle_across_m(cuda_device, M):
     np.testing.assert_allclose(got, want, **FP16_TOL)
 
 
+@pytest.mark.parametrize("M", [8, 24, 300])
+@pytest.mark.parametrize("group", [64, 256])
+def test_w4a16_other_group_sizes_follow_the_workspace_query(cuda_device, M, group):
+    """Groups of 64 (not a multiple of 128: decode-sized m takes the tensor-memory kernel instead of the streaming
+    one) and 256, through impl_cuda.run, i.e. with exactly the workspace the query reports."""
+    got, want = w4_case(M, 1024, 1024, seed=90 + M + group, device=cuda_device, group=group)
+    np.testing.assert_allclose(got, want, **FP16_TOL)
+    # the benchmark's weight shape, where the split-K choice is the interesting one
+    got, want = w4_case(M, 14336, 1024, seed=91 + M + group, device=cuda_device, group=group)
+    np.testing.assert_allclose(got, want, **FP16_TOL)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 128, 128), (16, 256, 384), (100, 128, 128), (128, 384, 256), (9, 256, 128)])
 def test_w4a16_short_k_fewer_blocks_than_issuers(cuda_device, M, N, K):
     """K of only 2-6 blocks of 64: some of the MMA issuer threads get no block and must contribute zero."""
@@ -195,6 +207,34 @@ def test_w4a16_config_shape_m4096_vs_torch_reference(cuda_device):
     status_clean()
     torch.testing.assert_close(out, impl_torch.run(*inputs), **FP16_TOL)
     assert torch.equal(out, impl_cuda.run(*inputs))     # deterministic, split-K or not
+
+
+@pytest.mark.parametrize("M,N", [(512, 10240), (300, 10240), (256, 1792), (200, 1792), (4096, 1280), (300, 640)])
+def test_w4a16_tail_units_are_bit_identical(cuda_device, monkeypatch, M, N):
+    """When the last wave of the persistent grid of 256-row tiles is at most half full, its tiles are cut into
+    two 128-row units.  A unit adds the same K blocks in the same order, so the result must equal the uncut
+    schedule bit for bit (TB200_W4_TAIL=0), ragged M and the non-TMA-store epilogue (odd column offset) included."""
+    ext = native.load()
+    K = 512
+    a, wp, sc, group, zp = tensors.generate_gemm_w4a16_inputs(M, K, N, device="cpu", seed=M + N)
+    ad, wpd, scd = a.to(cuda_device), wp.to(cuda_device), sc.to(cuda_device)
+    native.clear_device_status()
+    res = {}
+    for knob in ("1", "0"):
+        monkeypatch.setenv("TB200_W4_TAIL", knob)
+        out = torch.full((M, N + 8), 3.0, dtype=torch.float16, device=cuda_device)
+        ext.gemm_w4a16(ad, wpd, scd, out, group, zp, 0, None)
+        odd = torch.full((M, N + 8), 3.0, dtype=torch.float16, device=cuda_device)
+        ext.gemm_w4a16(ad, wpd, scd, odd, group, zp, 3, None)        # 6-byte column offset: stores from registers
+        torch.cuda.synchronize()
+        res[knob] = (out, odd)
+    status_clean()
+    assert torch.equal(res["1"][0], res["0"][0]) and torch.equal(res["1"][1], res["0"][1])
+    assert torch.equal(res["1"][0][:, :N], res["1"][1][:, 3:N + 3])
+    assert torch.all(res["1"][0][:, N:] == 3.0) and torch.all(res["1"][1][:, :3] == 3.0)
+    if N <= 1792:
+        want = ref_ops.gemm_w4a16(a.numpy(), wp.numpy(), sc.numpy(), group, zp).astype(np.float32)
+        np.testing.assert_allclose(res["1"][0][:, :N].float().cpu().numpy(), want, **FP16_TOL)
 
 
 @pytest.mark.parametrize("M", [64, 300])

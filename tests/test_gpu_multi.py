@@ -1,5 +1,6 @@
 """Two-GPU checks of the N-partitioned W4A16 GEMM (needs >= 2 GPUs; skipped on a single-GPU box):
-the NCCL gather and the fused epilogue gather must both reproduce the single-GPU result on every rank."""
+the NCCL gather, the push kernel and the fused epilogue gather must all reproduce the single-GPU result on
+every rank."""
 import os
 import socket
 
@@ -30,13 +31,14 @@ def _rank_main(rank, world, port, out_dir):
         lo, hi = npart.partition(N, world, rank)
         native.clear_device_status()
         via_nccl = npart.gemm_w4a16_partitioned(a, wp[lo:hi], sc[lo:hi], group, zp, gather="nccl")
+        pushed = npart.gemm_w4a16_partitioned(a, wp[lo:hi], sc[lo:hi], group, zp, gather="push").clone()
         fused = npart.gemm_w4a16_partitioned(a, wp[lo:hi], sc[lo:hi], group, zp, gather="fused")
         torch.cuda.synchronize()
         fused_copy = fused.clone()
         again = npart.gemm_w4a16_partitioned(a, wp[lo:hi], sc[lo:hi], group, zp, gather="fused")
         torch.cuda.synchronize()
         assert native.device_status()[0] == 0
-        torch.save({"nccl": via_nccl.cpu(), "fused": fused_copy.cpu(), "again": again.cpu()}, os.path.join(out_dir, f"r{rank}.pt"))
+        torch.save({"nccl": via_nccl.cpu(), "push": pushed.cpu(), "fused": fused_copy.cpu(), "again": again.cpu()}, os.path.join(out_dir, f"r{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -54,5 +56,6 @@ def test_two_gpu_partitioned_gemm_gathers_agree(tmp_path):
     for r in range(world):
         got = torch.load(tmp_path / f"r{r}.pt")
         assert torch.equal(got["nccl"], single), f"rank {r}: NCCL gather differs from the single-GPU result"
+        assert torch.equal(got["push"], single), f"rank {r}: push gather differs from the single-GPU result"
         assert torch.equal(got["fused"], single), f"rank {r}: fused gather differs from the single-GPU result"
         assert torch.equal(got["again"], single)

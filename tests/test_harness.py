@@ -28,7 +28,7 @@ def test_backend_registry():
 
 def test_case_counts_match_the_configs():
     want = {"dequant_int4_group": 1, "dequant_int8_channel": 3, "gemm_w4a16": 4, "gemm_fp8_blockscaled": 4,
-            "gemm_w4a16_npart": 12, "dequantize_rowwise": 20, "weight_dequant": 60, "quantize_fp8_block": 6, "matmul_int8": 20,
+            "gemm_w4a16_npart": 16, "dequantize_rowwise": 20, "weight_dequant": 60, "quantize_fp8_block": 6, "matmul_int8": 20,
             "matmul_fp32_fp16_fp8": 60, "quantize_int4_group": 6}
     assert sorted(list_operators()) == sorted(want)
     for op, n in want.items():

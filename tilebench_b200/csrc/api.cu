@@ -24,15 +24,34 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 int num_sms() {
-    static int cached[64] = {0};
+    static PerDeviceInt cached;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    int n = cached.v[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
+        cached.v[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
+}
+
+int current_device(int* dev) {
+    TB200_CUDA_TRY(cudaGetDevice(dev));
+    if (*dev < 0 || *dev >= kMaxDevices)
+        return fail(TB200_ERR_UNSUPPORTED, "device index %d is outside the library's per-device tables (0..%d)", *dev, kMaxDevices - 1);
+    return TB200_OK;
+}
+
+int ensure_max_smem(PerDeviceInt& done, const void* kern, int bytes) {
+    int dev = 0;
+    int rc = current_device(&dev);
+    if (rc != TB200_OK) return rc;
+    if (done.v[dev].load(std::memory_order_acquire) == 0) {
+        // setting the attribute twice from two racing threads is harmless; the flag only saves the call
+        TB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+        done.v[dev].store(1, std::memory_order_release);
+    }
+    return TB200_OK;
 }
 
 static std::vector<StatusHooks>& hooks() {

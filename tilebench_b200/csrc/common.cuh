@@ -11,6 +11,7 @@
 #include <stdint.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <atomic>
 
 #include "../../include/tb200.h"
 
@@ -21,6 +22,17 @@ int  fail(int code, const char* fmt, ...);          // stores the message, retur
 void clear_error();
 int  cuda_fail(cudaError_t e, const char* what);    // TB200_ERR_CUDA with the runtime's text
 int  num_sms();                                     // SM count of the current device (cached per device)
+
+// Per-device one-time set-up slots for launchers (thread-safe: two host threads making their first call
+// together both see a consistent value).  kMaxDevices bounds the device index; larger indices are refused.
+constexpr int kMaxDevices = 64;
+struct PerDeviceInt {
+    std::atomic<int> v[kMaxDevices];
+};
+// Current device index, or TB200_ERR_UNSUPPORTED (message set) when it does not fit the per-device tables.
+int current_device(int* dev);
+// Raises the dynamic shared-memory limit of `kern` on the current device the first time it is called there.
+int ensure_max_smem(PerDeviceInt& done, const void* kern, int bytes);
 
 #define TB200_CUDA_TRY(expr)                                              \
     do {                                                                  \
@@ -38,6 +50,7 @@ enum : int {
     ST_WAIT_TMEM_FULL = 3,   // drain warps waited for an accumulator that never completed
     ST_WAIT_TMEM_EMPTY = 4,  // MMA waited for an accumulator buffer that was never drained
     ST_WAIT_OPERAND = 5,     // MMA waited for a TMEM operand stage the convert warps never filled
+    ST_WAIT_SELFTEST = 6,    // the self-test kernel's wait on a barrier nobody arrives on (expected to run out)
 };
 
 // The status word lives in the library image (one copy per translation unit that launches
@@ -119,7 +132,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // The bound uses the SM-local cycle counter: reading it costs a few cycles, unlike the global
 // nanosecond timer.  On expiry it records `code` and returns false; the caller unwinds and exits.
 constexpr long long kWaitCycles = 1ll << 32;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code, int detail) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, int code, int detail, long long limit_cycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
@@ -127,10 +140,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int co
         for (int i = 0; i < 128; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
         }
-        if (clock64() - t0 > kWaitCycles) break;
+        if (clock64() - t0 > limit_cycles) break;
     }
     record_status(code, detail);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code, int detail) {
+    return mbar_wait_limit(bar, parity, code, detail, kWaitCycles);
 }
 
 // ---- TMA (tiled bulk tensor copy global -> shared, completion on an mbarrier) ----

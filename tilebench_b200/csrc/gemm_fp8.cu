@@ -476,12 +476,10 @@ template <int BN, typename Kern>
 static int launch_fp8(Kern kern, const void* a, const float* sa, const void* b, const float* sb, void* out, int64_t m,
                       int64_t n, int64_t k, int64_t ldo, cudaStream_t st) {
     using Cfg = Fp8Cfg<BN>;
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    TB200_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        TB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_set[dev] = true;
+    static PerDeviceInt attr_set;
+    {
+        const int rc_attr = ensure_max_smem(attr_set, reinterpret_cast<const void*>(kern), Cfg::kSmemBytes);
+        if (rc_attr != TB200_OK) return rc_attr;
     }
     CUtensorMap ta, tb, tb128;
     int rc = encode_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, m, k, k, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -511,11 +509,14 @@ static int launch_fp8(Kern kern, const void* a, const float* sa, const void* b, 
 static int launch_fp8_pair(const void* a, const float* sa, const void* b, const float* sb, void* out, int64_t m,
                            int64_t n, int64_t k, int64_t ldo, cudaStream_t st) {
     using Cfg = Fp8PairCfg;
-    static int max_pairs[64] = {0};
+    static PerDeviceInt max_pairs_tab;
     int dev = 0;
-    TB200_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return fail(TB200_ERR_DEVICE, "gemm_fp8_blockscaled: device index %d out of range", dev);
-    if (max_pairs[dev] == 0) {
+    {
+        const int rc_dev = current_device(&dev);
+        if (rc_dev != TB200_OK) return rc_dev;
+    }
+    int max_pairs = max_pairs_tab.v[dev].load(std::memory_order_acquire);
+    if (max_pairs == 0) {
         TB200_CUDA_TRY(cudaFuncSetAttribute(tb200_k_gemm_fp8_bs_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(num_sms() & ~1), 1, 1);
@@ -524,7 +525,8 @@ static int launch_fp8_pair(const void* a, const float* sa, const void* b, const 
         int clusters = 0;
         TB200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, tb200_k_gemm_fp8_bs_pair, &cfg));
         if (clusters < 1) return fail(TB200_ERR_UNSUPPORTED, "gemm_fp8_blockscaled: no CTA pair fits on this device");
-        max_pairs[dev] = clusters;
+        max_pairs = clusters;
+        max_pairs_tab.v[dev].store(clusters, std::memory_order_release);
     }
     CUtensorMap ta, tb;
     int rc = encode_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, m, k, k, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -532,7 +534,7 @@ static int launch_fp8_pair(const void* a, const float* sa, const void* b, const 
     rc = encode_tmap_2d(&tb, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k, k, 128, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TB200_OK) return rc;
     const int64_t tiles = ((m + 2 * kBM - 1) / (2 * kBM)) * (n / Cfg::kBN);
-    const int pairs = static_cast<int>(tiles < max_pairs[dev] ? tiles : max_pairs[dev]);
+    const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
     tb200_k_gemm_fp8_bs_pair<<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
         ta, tb, sa, sb, static_cast<__nv_bfloat16*>(out), static_cast<int>(m), static_cast<int>(n), static_cast<int>(k), ldo);
     TB200_CUDA_TRY(cudaGetLastError());

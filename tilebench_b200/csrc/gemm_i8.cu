@@ -362,12 +362,10 @@ template <int BN, typename Kern>
 static int launch_i8(Kern kern, const void* a, const void* b, void* out, int64_t m, int64_t n, int64_t k, int64_t ldo,
                      cudaStream_t st) {
     using Cfg = I8Cfg<BN>;
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    TB200_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        TB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_set[dev] = true;
+    static PerDeviceInt attr_set;
+    {
+        const int rc_attr = ensure_max_smem(attr_set, reinterpret_cast<const void*>(kern), Cfg::kSmemBytes);
+        if (rc_attr != TB200_OK) return rc_attr;
     }
     CUtensorMap ta, tb;
     int rc = encode_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, m, k, k, kI8BM, kI8StageRows, CU_TENSOR_MAP_SWIZZLE_64B);

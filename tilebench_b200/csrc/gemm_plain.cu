@@ -537,12 +537,10 @@ template <int KIND, int BN, typename Kern>
 static int launch_plain(Kern kern, const void* a, const void* b, void* out, int64_t m, int64_t n, int64_t k, int64_t ldo,
                         cudaStream_t st) {
     using Cfg = PlainCfg<KIND, BN>;
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    TB200_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        TB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_set[dev] = true;
+    static PerDeviceInt attr_set;
+    {
+        const int rc_attr = ensure_max_smem(attr_set, reinterpret_cast<const void*>(kern), Cfg::kSmemBytes);
+        if (rc_attr != TB200_OK) return rc_attr;
     }
     const CUtensorMapDataType dt = KIND == PK_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                  : KIND == PK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -566,11 +564,14 @@ static int launch_plain_pair(Kern kern, const void* a, const void* b, void* out,
                              cudaStream_t st) {
     using Cfg = PlainCfg<KIND, 256>;
     using PCfg = PlainPairCfg<KIND>;
-    static int max_pairs[64] = {0};
+    static PerDeviceInt max_pairs_tab;
     int dev = 0;
-    TB200_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return fail(TB200_ERR_DEVICE, "matmul_plain: device index %d out of range", dev);
-    if (max_pairs[dev] == 0) {
+    {
+        const int rc_dev = current_device(&dev);
+        if (rc_dev != TB200_OK) return rc_dev;
+    }
+    int max_pairs = max_pairs_tab.v[dev].load(std::memory_order_acquire);
+    if (max_pairs == 0) {
         TB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PCfg::kSmemBytes));
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(num_sms() & ~1), 1, 1);
@@ -579,7 +580,8 @@ static int launch_plain_pair(Kern kern, const void* a, const void* b, void* out,
         int clusters = 0;
         TB200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg));
         if (clusters < 1) return fail(TB200_ERR_UNSUPPORTED, "matmul_plain: no CTA pair fits on this device");
-        max_pairs[dev] = clusters;
+        max_pairs = clusters;
+        max_pairs_tab.v[dev].store(clusters, std::memory_order_release);
     }
     const CUtensorMapDataType dt = KIND == PK_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                  : KIND == PK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -591,7 +593,7 @@ static int launch_plain_pair(Kern kern, const void* a, const void* b, void* out,
                         KIND == PK_TF32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TB200_OK) return rc;
     const int64_t tiles = ((m + 2 * kPlBM - 1) / (2 * kPlBM)) * (n / 256);
-    const int pairs = static_cast<int>(tiles < max_pairs[dev] ? tiles : max_pairs[dev]);
+    const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
     kern<<<2 * pairs, Cfg::kThreads, PCfg::kSmemBytes, st>>>(ta, tb, static_cast<typename PlainTraits<KIND>::Out*>(out),
                                                               static_cast<int>(m), static_cast<int>(n), static_cast<int>(k), ldo);
     TB200_CUDA_TRY(cudaGetLastError());

@@ -36,6 +36,7 @@
 #include "common.cuh"
 
 #include <mutex>
+#include <stdlib.h>
 
 namespace tb200 {
 namespace {
@@ -90,9 +91,29 @@ struct PeerOut {
     __half* base[kMaxPeers];
 };
 
-struct Item { int n_blk, m_blk, kb0, kb1, ks; };
+// half < 0: the item covers all MT activation rows of tile m_blk; half = 0 / 1: a 128-row half of a 256-row
+// tile (tail of the persistent schedule, see Schedule below).
+struct Item { int n_blk, m_blk, kb0, kb1, ks, half; };
+// The persistent work list: `full` whole items (tile x K split), then 2 * tail_split half-height units that
+// cover the last tail_split tiles.  When the last wave of the grid would hold at most half a grid of
+// 256-row tiles, cutting them in two lets twice as many SMs share that wave (6.05 -> 6.5 instead of 7
+// waves for 896 tiles on 148 SMs).  A half unit adds the same K blocks in the same order into the same
+// accumulator columns, so results do not depend on where the cut falls.
+struct Schedule { int tiles_n, tiles_m, splitk, KB, tail_split, items; };
+__device__ __forceinline__ Schedule make_schedule(int tiles_n, int tiles_m, int splitk, int KB, int tail_split) {
+    Schedule sc{tiles_n, tiles_m, splitk, KB, tail_split, tiles_n * tiles_m * splitk + tail_split};
+    return sc;
+}
 // tiles_m counts activation tiles of MT rows.
-__device__ __forceinline__ Item make_item(int w, int tiles_n, int tiles_m, int splitk, int KB) {
+__device__ __forceinline__ Item make_item(int w, const Schedule& sc) {
+    const int tiles_n = sc.tiles_n, tiles_m = sc.tiles_m, splitk = sc.splitk, KB = sc.KB;
+    int half = -1;
+    const int full = tiles_n * tiles_m * splitk - sc.tail_split;      // tail_split > 0 only with splitk == 1
+    if (w >= full) {
+        const int j = w - full;
+        w = full + (j >> 1);
+        half = j & 1;
+    }
     const int tile = w / splitk;
     const int ks = w - tile * splitk;
     const int per_group = kGroupN * tiles_m;
@@ -104,6 +125,7 @@ __device__ __forceinline__ Item make_item(int w, int tiles_n, int tiles_m, int s
     it.n_blk = first_n + r % gsz;
     it.m_blk = r / gsz;
     it.ks = ks;
+    it.half = half;
     it.kb0 = static_cast<int>(static_cast<int64_t>(ks) * KB / splitk);
     it.kb1 = static_cast<int>(static_cast<int64_t>(ks + 1) * KB / splitk);
     return it;
@@ -124,12 +146,12 @@ __device__ __forceinline__ uint32_t dq_pair(uint32_t lo, uint32_t hi, uint32_t s
 using namespace tb200;
 
 template <int MT>
-__device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ tmap_act, const CUtensorMap* __restrict__ tmap_w,
-                                                const CUtensorMap* __restrict__ tmap_out,
+__device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ tmap_act, const CUtensorMap* __restrict__ tmap_act_half,
+                                                const CUtensorMap* __restrict__ tmap_w, const CUtensorMap* __restrict__ tmap_out,
                                                 const __half* __restrict__ scales, __half* __restrict__ out,
                                                 float* __restrict__ ws, int M, int N, int K, int groups_per_row,
                                                 int kb_per_group, int64_t ldo, int64_t col_offset, int splitk,
-                                                float zp_plus_1024, int tma_store, const PeerOut& peers) {
+                                                float zp_plus_1024, int tma_store, int tail_split, const PeerOut& peers) {
     using Cfg = W4Cfg<MT>;
     constexpr int SA = Cfg::kSA;
     constexpr int SW = Cfg::kSW;
@@ -156,7 +178,8 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
     const int KB = K / kBK;
     const int tiles_n = N / kBNW;
     const int tiles_m = (M + MT - 1) / MT;
-    const int items = tiles_n * tiles_m * splitk;
+    const Schedule sched = make_schedule(tiles_n, tiles_m, splitk, KB, MT == 256 ? tail_split : 0);
+    const int items = sched.items;
     // accumulator of an item and how often it was used before (phase of its barriers)
     auto acc_of = [](uint32_t item_cnt) { return NACC == 1 ? 0 : static_cast<int>(item_cnt & 1); };
     auto acc_use = [](uint32_t item_cnt) { return NACC == 1 ? item_cnt : (item_cnt >> 1); };
@@ -168,6 +191,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         for (int b = 0; b < 2; ++b) { mbar_init(&bar_dfull[b], NI); mbar_init(&bar_dempty[b], 4); }
         mbar_fence_init();
         tma_prefetch_desc(tmap_act);
+        if (MT == 256 && tail_split > 0) tma_prefetch_desc(tmap_act_half);
         tma_prefetch_desc(tmap_w);
         if (Cfg::kTmaStore && tma_store) tma_prefetch_desc(tmap_out);
     }
@@ -186,12 +210,17 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
             uint32_t it = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
-                const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
+                const Item im = make_item(w, sched);
                 for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
                     const int s = it % SA;
                     if (!mbar_wait(&bar_done[s], ((it / SA) & 1) ^ 1, ST_WAIT_SMEM_EMPTY, kb)) { ok = false; break; }
-                    mbar_expect_tx(&bar_afull[s], Cfg::kActStageBytes);
-                    tma_load_2d(act_ring + s * Cfg::kActStageBytes, tmap_act, &bar_afull[s], kb * kBK, im.m_blk * MT);
+                    if (MT == 256 && im.half >= 0) {      // 128-row unit: the upper or lower half of the stage's box
+                        mbar_expect_tx(&bar_afull[s], Cfg::kActStageBytes / 2);
+                        tma_load_2d(act_ring + s * Cfg::kActStageBytes, tmap_act_half, &bar_afull[s], kb * kBK, im.m_blk * MT + im.half * 128);
+                    } else {
+                        mbar_expect_tx(&bar_afull[s], Cfg::kActStageBytes);
+                        tma_load_2d(act_ring + s * Cfg::kActStageBytes, tmap_act, &bar_afull[s], kb * kBK, im.m_blk * MT);
+                    }
                 }
             }
             if (!ok) {   // give copies already in flight a bounded chance to land before the CTA exits
@@ -209,7 +238,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
             uint32_t it = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
-                const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
+                const Item im = make_item(w, sched);
                 for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
                     const int s = it % SW;
                     if (!mbar_wait(&bar_wempty[s], ((it / SW) & 1) ^ 1, ST_WAIT_SMEM_EMPTY, -kb - 1)) { ok = false; break; }
@@ -230,12 +259,14 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         // ---------------- MMA issuers ----------------
         if (lane == 0) {
             const int me = warp - Cfg::kMmaWarp0;                    // K blocks with it % NI == me are mine
-            constexpr uint32_t idesc = umma_idesc(0, 0, kBNW, MT);   // f16 x f16 -> f32, M = 128, N = MT
+            constexpr uint32_t idesc_full = umma_idesc(0, 0, kBNW, MT);   // f16 x f16 -> f32, M = 128, N = MT
+            constexpr uint32_t idesc_half = umma_idesc(0, 0, kBNW, 128);  // N = 128 for a half unit of the 256-row tile
             uint32_t it = 0, item_cnt = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++item_cnt) {
-                const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
+                const Item im = make_item(w, sched);
                 const int acc = acc_of(item_cnt);
+                const uint32_t idesc = (MT == 256 && im.half >= 0) ? idesc_half : idesc_full;
                 const uint32_t d_tmem = tmem_base + (acc * NI + me) * MT;
                 // the accumulator set must have been drained before this item's first MMA overwrites it
                 if (!mbar_wait(&bar_dempty[acc], (acc_use(item_cnt) & 1) ^ 1, ST_WAIT_TMEM_EMPTY, w)) { ok = false; break; }
@@ -279,7 +310,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         // three of the next work item while the current one runs, so no load sits on the K loop.
         __half s0, s1, s2, n0 = __half(), n1 = __half(), n2 = __half();
         if (static_cast<int>(blockIdx.x) < items) {
-            const Item im = make_item(blockIdx.x, tiles_n, tiles_m, splitk, KB);
+            const Item im = make_item(blockIdx.x, sched);
             const __half* srow = scale_row(im);
             const int g = im.kb0 / kb_per_group;
             n0 = scale_at(srow, g); n1 = scale_at(srow, g + 1); n2 = scale_at(srow, g + 2);
@@ -287,12 +318,12 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         uint32_t it = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
-            const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
+            const Item im = make_item(w, sched);
             const __half* srow = scale_row(im);
             int gcur = im.kb0 / kb_per_group;
             s0 = n0; s1 = n1; s2 = n2;
             if (w + static_cast<int>(gridDim.x) < items) {
-                const Item nx = make_item(w + gridDim.x, tiles_n, tiles_m, splitk, KB);
+                const Item nx = make_item(w + gridDim.x, sched);
                 const __half* nrow = scale_row(nx);
                 const int g = nx.kb0 / kb_per_group;
                 n0 = scale_at(nrow, g); n1 = scale_at(nrow, g + 1); n2 = scale_at(nrow, g + 2);
@@ -342,7 +373,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         bool ok = true;
         bool store_pending = false;
         for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++item_cnt) {
-            const Item im = make_item(w, tiles_n, tiles_m, splitk, KB);
+            const Item im = make_item(w, sched);
             const int acc = acc_of(item_cnt);
             // issuer i wrote its accumulator in this item iff one of the item's K blocks (global
             // numbers it0 .. it0 + len - 1) is congruent to i modulo NI
@@ -378,9 +409,12 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 // column of a [128 m x 128 n] fp16 tile in shared memory (a warp writes 64 contiguous
                 // bytes per m), and one TMA store per 128 rows of m moves the tile out, clipped at M.
                 __half* tile = reinterpret_cast<__half*>(store_tile);
+                const int passes = (MT == 256 && im.half >= 0) ? 1 : MT / 128;   // 128-row passes over the accumulator
+                const int first_half = im.half >= 0 ? im.half : 0;
 #pragma unroll 1
-                for (int h = 0; h < MT / 128; ++h) {
-                    if (im.m_blk * MT + h * 128 >= M) break;
+                for (int h = 0; h < passes; ++h) {
+                    const int row0 = im.m_blk * MT + (first_half + h) * 128;
+                    if (row0 >= M) break;
                     if (store_pending) {                     // the previous store must have read the tile
                         if (epi_tid == 0) tma_store_wait_read<0>();
                         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -390,7 +424,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                     for (int c = 0; c < 4; ++c) {
                         uint32_t v[32];
                         load_sum(h * 128 + c * 32, v);
-                        if (h == MT / 128 - 1 && c == 3) {   // accumulator fully read: release it
+                        if (h == passes - 1 && c == 3) {     // accumulator fully read: release it
                             tc_fence_before();
                             __syncwarp();
                             if (lane == 0) mbar_arrive(&bar_dempty[acc]);
@@ -401,13 +435,12 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                     fence_async_smem();
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     if (epi_tid == 0) {
-                        tma_store_2d(tmap_out, tile, im.n_blk * kBNW, im.m_blk * MT + h * 128);
+                        tma_store_2d(tmap_out, tile, im.n_blk * kBNW, row0);
                         tma_store_commit();
                     }
                     store_pending = true;
                     if (peers.count > 0) {
                         // the same tile to every other rank: 16 threads write one 256-byte row, 128-bit stores
-                        const int row0 = im.m_blk * MT + h * 128;
                         const int rows_valid = min(128, M - row0);
                         for (int p = 0; p < peers.count; ++p) {
                             __half* dst = peers.base[p] + static_cast<int64_t>(row0) * ldo + im.n_blk * kBNW;
@@ -419,17 +452,19 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                         }
                     }
                 }
-                // an item whose upper half lies beyond M never reached the release above
-                if ((MT / 128 - 1) * 128 + im.m_blk * MT >= M) {
+                // an item whose last pass lies beyond M never reached the release above
+                if (im.m_blk * MT + (first_half + passes - 1) * 128 >= M) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bar_dempty[acc]);
                 }
             } else {
+                const int unit_rows = (MT == 256 && im.half >= 0) ? 128 : MT;
+                const int unit_row0 = im.m_blk * MT + (im.half > 0 ? 128 : 0);
 #pragma unroll
                 for (int c = 0; c < MT / kChunk; ++c) {
-                    const int m0 = im.m_blk * MT + c * kChunk;
-                    if (m0 < M) {
+                    const int m0 = unit_row0 + c * kChunk;
+                    if (c * kChunk < unit_rows && m0 < M) {
                         uint32_t v[kChunk];
                         load_sum(c * kChunk, v);
                         if (splitk == 1) {
@@ -465,12 +500,12 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
 
 #define TB200_W4_KERNEL(MT)                                                                                        \
     extern "C" __global__ void __launch_bounds__(W4Cfg<MT>::kThreads, 1) tb200_k_gemm_w4a16_m##MT(                 \
-        const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_w,                  \
-        const __grid_constant__ CUtensorMap tmap_out, const __half* scales, __half* out, float* ws, int M, int N,  \
-        int K, int gpr, int kbpg, int64_t ldo, int64_t col_offset, int splitk, float zp1024, int tma_store,        \
-        const PeerOut peers) {                                                                                     \
-        gemm_w4a16_body<MT>(&tmap_act, &tmap_w, &tmap_out, scales, out, ws, M, N, K, gpr, kbpg, ldo, col_offset,   \
-                            splitk, zp1024, tma_store, peers);                                                     \
+        const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_act_half,           \
+        const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_out,                  \
+        const __half* scales, __half* out, float* ws, int M, int N, int K, int gpr, int kbpg, int64_t ldo,         \
+        int64_t col_offset, int splitk, float zp1024, int tma_store, int tail_split, const PeerOut peers) {        \
+        gemm_w4a16_body<MT>(&tmap_act, &tmap_act_half, &tmap_w, &tmap_out, scales, out, ws, M, N, K, gpr, kbpg,    \
+                            ldo, col_offset, splitk, zp1024, tma_store, tail_split, peers);                        \
     }
 TB200_W4_KERNEL(16)
 TB200_W4_KERNEL(64)
@@ -519,7 +554,10 @@ bool use_gemv(int64_t m, int64_t group) { return m <= kGemvMaxM && group % 128 =
 // also guarantees each MMA issuer thread its own block.
 int pick_splitk(int64_t m, int64_t n, int64_t k) {
     const int mt = pick_mt(m);
-    if (mt > 64) return 1;
+    // m <= 16 never splits K: with group a multiple of 128 those shapes take the streaming kernel, and with
+    // any other group the tensor-memory kernel runs unsplit, so that the workspace query (which does not
+    // know the group) can promise "no workspace" for every decode-sized call
+    if (mt > 64 || m <= kGemvMaxM) return 1;
     const int64_t tiles = (n / kBNW) * ((m + mt - 1) / mt);
     const int sms = num_sms();
     const int64_t KB = k / kBK;
@@ -540,12 +578,10 @@ int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void
               int64_t k, int64_t group, int zp, int64_t ldo, int64_t col_offset, int splitk, const PeerOut& peers,
               cudaStream_t st) {
     using Cfg = W4Cfg<MT>;
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    TB200_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        TB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_set[dev] = true;
+    static PerDeviceInt attr_set;
+    {
+        const int rc_attr = ensure_max_smem(attr_set, reinterpret_cast<const void*>(kern), Cfg::kSmemBytes);
+        if (rc_attr != TB200_OK) return rc_attr;
     }
     CUtensorMap ta, tw, to;
     int rc = encode_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, m, k, k * 2, MT, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -564,12 +600,26 @@ int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void
     } else {
         to = ta;   // unused by the kernel
     }
-    const int64_t items = (n / kBNW) * ((m + MT - 1) / MT) * splitk;
+    int64_t items = (n / kBNW) * ((m + MT - 1) / MT) * splitk;
+    // 256-row tiles: when the last wave of the persistent grid would be at most half full, its tiles are cut
+    // into two 128-row units each (see Schedule).  TB200_W4_TAIL=0 turns the cut off (tests compare both).
+    int tail_split = 0;
+    CUtensorMap tah = ta;
+    if (MT == 256 && splitk == 1) {
+        const int64_t rem = items % num_sms();
+        const char* knob = getenv("TB200_W4_TAIL");
+        if (rem > 0 && 2 * rem <= num_sms() && !(knob && knob[0] == '0')) {
+            tail_split = static_cast<int>(rem);
+            rc = encode_tmap_2d(&tah, a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, m, k, k * 2, 128, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+            if (rc != TB200_OK) return rc;
+        }
+    }
+    items += tail_split;
     const int grid = static_cast<int>(items < num_sms() ? items : num_sms());
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(ta, tw, to, static_cast<const __half*>(scales), static_cast<__half*>(out), ws,
+    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(ta, tah, tw, to, static_cast<const __half*>(scales), static_cast<__half*>(out), ws,
                                                         static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
                                                         static_cast<int>(k / group), static_cast<int>(group / kBK), ldo,
-                                                        col_offset, splitk, 1024.0f + static_cast<float>(zp), tma_store, peers);
+                                                        col_offset, splitk, 1024.0f + static_cast<float>(zp), tma_store, tail_split, peers);
     TB200_CUDA_TRY(cudaGetLastError());
     if (splitk > 1) {
         const int64_t total = m * (n / 4);
@@ -587,7 +637,7 @@ int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void
 
 extern "C" size_t tb200_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (m <= 0 || n <= 0 || k <= 0 || n % kBNW != 0 || k % 128 != 0) return 0;
-    if (m <= kGemvMaxM) return 0;                 // streaming kernel: no split-K scratch
+    if (m <= kGemvMaxM) return 0;                 // streaming kernel or unsplit tensor-memory kernel: no scratch
     const int s = pick_splitk(m, n, k);
     return s > 1 ? static_cast<size_t>(s) * m * n * sizeof(float) : 0;
 }

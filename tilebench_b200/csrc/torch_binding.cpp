@@ -150,6 +150,21 @@ void gemm_w4a16_gather(const torch::Tensor& a, const torch::Tensor& wp, const to
              "tb200_gemm_w4a16_gather");
 }
 
+// Pushes `local` [m, n_local] into columns [rank * n_local, ...) of every rank's full [m, ldo] buffer.
+void allgather_cols(const torch::Tensor& local, const std::vector<int64_t>& out_ptrs, int64_t rank, int64_t ldo) {
+    TORCH_CHECK(local.is_cuda() && local.dim() == 2 && local.stride(1) == 1, "local must be a CUDA matrix with unit column stride");
+    std::vector<void*> ptrs;
+    for (int64_t p : out_ptrs) ptrs.push_back(reinterpret_cast<void*>(static_cast<uintptr_t>(p)));
+    c10::cuda::CUDAGuard guard(local.device());
+    check_rc(tb200_allgather_cols(local.data_ptr(), local.stride(0), ptrs.data(), static_cast<int>(ptrs.size()), static_cast<int>(rank),
+                                  local.size(0), local.size(1), local.element_size(), ldo, stream_of(local)),
+             "tb200_allgather_cols");
+}
+
+void selftest_bounded_wait(int64_t limit_cycles) {
+    check_rc(tb200_selftest_bounded_wait(limit_cycles, at::cuda::getCurrentCUDAStream().stream()), "tb200_selftest_bounded_wait");
+}
+
 void quantize_fp8_block(const torch::Tensor& x, torch::Tensor& q, torch::Tensor& scales, int64_t block_rows) {
     check_cuda(x, "x", torch::kFloat32);
     check_cuda(q, "q", torch::kFloat8_e4m3fn);
@@ -226,6 +241,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_w4a16_workspace_bytes", &gemm_w4a16_workspace_bytes);
     m.def("gemm_w4a16", &gemm_w4a16);
     m.def("gemm_w4a16_gather", &gemm_w4a16_gather);
+    m.def("allgather_cols", &allgather_cols);
+    m.def("selftest_bounded_wait", &selftest_bounded_wait);
     m.def("quantize_fp8_block", &quantize_fp8_block);
     m.def("matmul_int8_packed2", &matmul_int8_packed2);
     m.def("matmul_plain", &matmul_plain);

@@ -23,6 +23,7 @@ ABI_SYMBOLS = (
     "tb200_device_status", "tb200_clear_device_status",
     "tb200_gemm_w4a16_static_scratch_bytes", "tb200_gemm_w4a16_static", "tb200_gemm_w4a16_gather",
     "tb200_quantize_fp8_block", "tb200_matmul_int8_packed2", "tb200_matmul_plain", "tb200_quantize_int4_group",
+    "tb200_allgather_cols", "tb200_selftest_bounded_wait",
 )
 
 DT_F32, DT_F16, DT_BF16, DT_F8E4M3 = 0, 1, 2, 3
@@ -58,6 +59,9 @@ def load():
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     sys.modules[EXT_STEM] = mod
+    import torch
+    if torch.cuda.is_available():
+        mod.check_device()      # sm_100 only: refuse here, not with a "no kernel image" error at the first launch
     _ext = mod
     return mod
 
@@ -95,6 +99,10 @@ def capi() -> ctypes.CDLL:
     lib.tb200_matmul_plain.restype = ci
     lib.tb200_quantize_int4_group.argtypes = [vp, vp, vp, i64, i64, i64, ci, vp]
     lib.tb200_quantize_int4_group.restype = ci
+    lib.tb200_allgather_cols.argtypes = [vp, i64, ctypes.POINTER(vp), ci, ci, i64, i64, i64, i64, vp]
+    lib.tb200_allgather_cols.restype = ci
+    lib.tb200_selftest_bounded_wait.argtypes = [i64, vp]
+    lib.tb200_selftest_bounded_wait.restype = ci
     lib.tb200_device_status.argtypes = [ctypes.POINTER(ci), ctypes.POINTER(ci)]
     lib.tb200_clear_device_status.argtypes = []
     for name in ("tb200_dequant_int4_group", "tb200_dequant_int8_rowwise", "tb200_weight_dequant_block",
@@ -110,7 +118,8 @@ def last_error() -> str:
 
 
 def require_b200() -> None:
-    """Raise unless the current device is sm_100; called by every impl_cuda.run."""
+    """Raise unless the current device is sm_100.  load() makes the same check once when a GPU is present;
+    callers that switch devices afterwards call this again."""
     load().check_device()
 
 

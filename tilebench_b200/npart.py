@@ -4,13 +4,18 @@ the plumbing, no data-path collective unless a replicated result is asked for.
   partition(n, world, rank)        rows [lo, hi) of the weight a rank owns (128-row tiles never straddle)
   gemm_w4a16_partitioned(...)      local GEMM on the rank's slice; gather=True all-gathers the column
                                    slices into [M, N] on every rank
-Two gathers:
+Three gathers:
   "fused"  the GEMM epilogue stores every finished tile into the output buffer of EVERY rank
            (tb200_gemm_w4a16_gather: TMA store locally, 128-bit peer stores over NVLink), so the transfer
            overlaps the main loop.  The [M, N] output lives in a symmetric-memory buffer that is
            allocated once per shape and reused (peers must have it mapped before the call).
-  "nccl"   one NCCL all-gather of the contiguous per-rank slices [M, N/G] into a staging buffer
-           [G, M, N/G], then one interleave pass into a fresh row-major [M, N].
+  "push"   the GEMM writes its slice in place into this rank's symmetric [M, N] buffer, then one streaming
+           kernel (tb200_allgather_cols) pushes the slice into the same columns of every peer's buffer:
+           slices land at their final strided place, no staging buffer and no interleave pass.  The
+           unfused counterpart of "fused" (compute, then exchange).
+  "nccl"   the library baseline: one NCCL all-gather of the contiguous per-rank slices [M, N/G] into a
+           staging buffer [G, M, N/G], then one interleave pass into a row-major [M, N].  NCCL moves
+           contiguous buffers only, so the strided landing costs that extra pass.
 `partitioned_reference` runs the same partition -> local op -> gather path with any local function
 and any backend (gloo on CPU), which is how the host logic is tested without GPUs.
 """
@@ -70,6 +75,26 @@ def symmetric_output(m: int, n: int, device) -> tuple:
     return _symm_cache[key]
 
 
+def gemm_w4a16_push_gather(a, wp_local, scales_local, group_size: int = 128, zp: int = 8, workspace=None):
+    """out = a @ dequant(wp)^T on every rank: local GEMM into this rank's columns of the symmetric buffer, then
+    one push kernel to the peers.  Returns the shared buffer (overwritten by the next call)."""
+    from tilebench_b200 import native
+    ext = native.load()
+    world, rank = world_and_rank()
+    m, k = a.shape
+    n_local = wp_local.shape[0]
+    n = n_local * world
+    out, hdl = symmetric_output(m, n, a.device)
+    ws_bytes = ext.gemm_w4a16_workspace_bytes(m, n_local, k)
+    if ws_bytes and workspace is None:
+        workspace = torch.empty(ws_bytes // 4, dtype=torch.float32, device=a.device)
+    hdl.barrier()            # every rank is done reading the previous contents
+    ext.gemm_w4a16(a, wp_local.contiguous(), scales_local.contiguous(), out, int(group_size), int(zp), rank * n_local, workspace)
+    ext.allgather_cols(out[:, rank * n_local:(rank + 1) * n_local], [int(p) for p in hdl.buffer_ptrs], rank, n)
+    hdl.barrier()            # every rank's stores have landed
+    return out
+
+
 def gemm_w4a16_fused_gather(a, wp_local, scales_local, group_size: int = 128, zp: int = 8):
     """out = a @ dequant(wp)^T on every rank, the all-gather done by the GEMM's epilogue (see module doc).
     Returns the shared symmetric buffer: its contents are overwritten by the next call."""
@@ -87,16 +112,21 @@ def gemm_w4a16_fused_gather(a, wp_local, scales_local, group_size: int = 128, zp
 
 
 def gemm_w4a16_partitioned(a, wp_local, scales_local, group_size: int = 128, zp: int = 8, gather=True,
-                           workspace=None):
+                           workspace=None, out_local=None):
     """This rank's slice of out = a @ dequant(wp)^T, or the full [M, N]: gather=True / "nccl" gathers with
-    NCCL into a fresh tensor, gather="fused" uses the epilogue peer stores (m > 64, world > 1)."""
+    NCCL into a fresh tensor, gather="fused" uses the epilogue peer stores (m > 64, world > 1), gather="push"
+    the separate push kernel.  `out_local` ([M, n_local] fp16) and `workspace` may be passed in to keep
+    allocation out of a timed loop."""
     from tilebench_b200 import native
     ext = native.load()
     m, k = a.shape
     n_local = wp_local.shape[0]
     if gather == "fused" and world_and_rank()[0] > 1 and m > 64:
         return gemm_w4a16_fused_gather(a, wp_local, scales_local, group_size, zp)
-    out_local = torch.empty((m, n_local), dtype=torch.float16, device=a.device)
+    if gather == "push" and world_and_rank()[0] > 1:
+        return gemm_w4a16_push_gather(a, wp_local, scales_local, group_size, zp, workspace)
+    if out_local is None:
+        out_local = torch.empty((m, n_local), dtype=torch.float16, device=a.device)
     ws_bytes = ext.gemm_w4a16_workspace_bytes(m, n_local, k)
     if ws_bytes and workspace is None:
         workspace = torch.empty(ws_bytes // 4, dtype=torch.float32, device=a.device)
