@@ -24,37 +24,48 @@ def _gen(seed: int) -> torch.Generator:
     return torch.Generator(device="cpu").manual_seed(int(seed))
 
 
-def _normalize_sequence(values, name):
-    if isinstance(values, dict) and "expr" in values:
-        result = eval(values["expr"])  # noqa: S307  (package-internal configs only)
-        if not isinstance(result, (list, tuple)) or len(result) == 0:
-            raise ValueError(f"case_grid expr for '{name}' must evaluate to a non-empty list.")
-        return list(result)
-    if not isinstance(values, (list, tuple)) or len(values) == 0:
-        raise ValueError(f"case_grid field '{name}' must be a non-empty list/tuple.")
-    return list(values)
+class CaseGridError(ValueError):
+    """A case_grid / test_cases block that cannot be expanded."""
+
+
+def _axis_values(spec, axis: str) -> list:
+    """Candidate values of one grid axis.  An axis is written either as a plain list or as
+    `{expr: "<python>"}`, a Python expression yielding the list (the configs shipped with the package use it for
+    arithmetic progressions such as `[1024 * i for i in range(1, 21)]`)."""
+    if isinstance(spec, dict) and "expr" in spec:
+        spec = eval(spec["expr"], {"__builtins__": __builtins__}, {})  # noqa: S307 - configs are package files, not user input
+        origin = "expr of axis"
+    else:
+        origin = "axis"
+    if isinstance(spec, (list, tuple)) and len(spec) > 0:
+        return list(spec)
+    raise CaseGridError(f"case_grid: {origin} '{axis}' needs a non-empty list of candidates, got {spec!r}")
 
 
 def _expand_case_grid(case_grid, case_defaults=None):
-    if not isinstance(case_grid, dict) or len(case_grid) == 0:
-        raise ValueError("case_grid must be a non-empty mapping of parameter -> candidate list.")
-    keys = list(case_grid)
-    lists = [_normalize_sequence(case_grid[k], k) for k in keys]
-    cases = []
-    for combo in product(*lists):
-        case = dict(case_defaults or {})
-        case.update(zip(keys, combo))
-        cases.append(case)
-    return cases
+    """Cartesian product of the grid axes, in the order the config lists them (last axis fastest), each case
+    laid over a copy of `case_defaults`."""
+    if not isinstance(case_grid, dict) or not case_grid:
+        raise CaseGridError("case_grid has to map at least one parameter name to its candidates")
+    axes = [(axis, _axis_values(spec, axis)) for axis, spec in case_grid.items()]
+    names = [axis for axis, _ in axes]
+    base = dict(case_defaults or {})
+    return [{**base, **dict(zip(names, point))} for point in product(*(vals for _, vals in axes))]
+
+
+# kept under the reference's name for callers that expand a single axis
+_normalize_sequence = _axis_values
 
 
 def expand_cases(operator_name, config):
-    """Priority: explicit test_cases, then case_grid over case_defaults."""
-    if config.get("test_cases"):
-        return list(config["test_cases"])
-    if "case_grid" in config:
-        return _expand_case_grid(config["case_grid"], config.get("case_defaults", {}))
-    raise ValueError(f"Operator '{operator_name}' config must define test_cases or case_grid.")
+    """The operator's case list: `test_cases` verbatim when given, else `case_grid` expanded over `case_defaults`."""
+    explicit = config.get("test_cases")
+    if explicit:
+        return list(explicit)
+    grid = config.get("case_grid")
+    if grid is not None:
+        return _expand_case_grid(grid, config.get("case_defaults"))
+    raise CaseGridError(f"operator '{operator_name}': the config defines neither test_cases nor case_grid")
 
 
 # ---- quantised-weight inputs ------------------------------------------------------------------

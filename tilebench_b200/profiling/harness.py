@@ -29,7 +29,6 @@ def main() -> None:
     ap.add_argument("--case", default="{}", help="JSON overrides of the operator's case_defaults")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--seed", type=int, default=1)
-    ap.add_argument("--device-inputs", action="store_true", help="draw the inputs on the GPU (large cases)")
     args = ap.parse_args()
 
     cfg = yaml.safe_load(open(operator_config(args.operator)))
