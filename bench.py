@@ -75,6 +75,23 @@ def load_peaks():
     return peaks
 
 
+def fill_tensor_fractions(rows, peaks):
+    """frac_of_tensor_peak (burst) and frac_of_sustained_peak of every tensor-bound row, from the measured
+    library-GEMM rate of the row's input type."""
+    for r in rows:
+        kind = r.get("peak_kind")
+        if not kind:
+            continue
+        scale = r.pop("peak_scale", 1)
+        pk = peaks["tflops"].get(kind)
+        if pk:
+            r.update(frac_of_tensor_peak=r["TFLOPs"] / (scale * pk["burst"]), frac_of_sustained_peak=r["TFLOPs"] / (scale * pk["sustained"]),
+                     tensor_peak=f"{'%d x ' % scale if scale != 1 else ''}{kind}: {pk['burst']:.0f} burst / {pk['sustained']:.0f} sustained TFLOPS, {pk['source']}")
+        else:
+            r.update(frac_of_tensor_peak=None, tensor_peak=f"{kind}: no measured peak available")
+    return rows
+
+
 def add_live_peaks(peaks, kinds=("fp8_e4m3fn", "int8", "tf32"), sustained_s=1.5):
     """The tensor-core denominators the driver's file lacks, measured now on this GPU with the library GEMMs
     (tilebench_b200.measure_peak: torch._scaled_mm e4m3, torch._int_mm, TF32 matmul; burst and a short loop).
@@ -171,7 +188,11 @@ def event_time_ms(torch, fn, iters: int) -> float:
 
 def time_rotating(torch, make_call, sets: int, warmup: int, iters: int) -> float:
     """ms per call over back-to-back calls that rotate through `sets` independent buffer sets
-    (their combined footprint exceeds L2, so no call finds its operands cached)."""
+    (their combined footprint exceeds L2, so no call finds its operands cached).
+
+    One rotation is captured into a CUDA graph and the replay is timed, so the figure is device time: kernels
+    of 5-40 us would otherwise be paced by how fast the host can launch them (which differs from box to box).
+    If capture fails the rotation is launched eagerly."""
     calls = [make_call(i) for i in range(sets)]
     for _ in range(warmup):
         for c in calls:
@@ -181,7 +202,23 @@ def time_rotating(torch, make_call, sets: int, warmup: int, iters: int) -> float
     def rotation():
         for c in calls:
             c()
-    return event_time_ms(torch, rotation, iters) / sets
+    runner = rotation
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            rotation()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            rotation()
+        graph.replay()
+        torch.cuda.synchronize()
+        runner = graph.replay
+    except Exception:
+        torch.cuda.synchronize()
+    return event_time_ms(torch, runner, iters) / sets
 
 
 def sections(torch, dev, peaks, world, rank, steps, warmup):
@@ -205,13 +242,8 @@ def sections(torch, dev, peaks, world, rank, steps, warmup):
         """`kind` names the measured library-GEMM rate that bounds the row (bf16, fp16, tf32, fp8_e4m3fn, int8);
         `scale` multiplies it (aggregate rows over several GPUs)."""
         tf = flops / (ms * 1e-3) / 1e12
-        pk = peaks["tflops"].get(kind)
-        r = {"name": name, "ms": ms, "TFLOPs": tf, "bound": "tensor", "launches_per_call": launches}
-        if pk:
-            r.update(frac_of_tensor_peak=tf / (scale * pk["burst"]), frac_of_sustained_peak=tf / (scale * pk["sustained"]),
-                     tensor_peak=f"{'%d x ' % scale if scale != 1 else ''}{kind}: {pk['burst']:.0f} burst / {pk['sustained']:.0f} sustained TFLOPS, {pk['source']}")
-        else:
-            r.update(frac_of_tensor_peak=None, tensor_peak=f"{kind}: no measured peak available")
+        r = {"name": name, "ms": ms, "TFLOPs": tf, "bound": "tensor", "launches_per_call": launches, "peak_kind": kind,
+             "peak_scale": scale}
         if nbytes:
             r["GBps"] = nbytes / (ms * 1e-3) / 1e9
             r["frac_of_hbm_peak"] = r["GBps"] / peaks["hbm_gbs"]
@@ -500,8 +532,9 @@ def run_ours(args):
         del w, out
         torch.cuda.empty_cache()
         try:
-            add_live_peaks(peaks)
             extra = sections(torch, dev, peaks, world, rank, args.steps, args.warmup)
+            add_live_peaks(peaks)               # after the sections, so the probes' seconds-long loops do not pre-heat them
+            fill_tensor_fractions(extra, peaks)
         except Exception as e:  # a failing section must not lose the headline
             extra = [{"name": "sections", "error": f"{type(e).__name__}: {e}"}]
     sampler.busy(False)

@@ -167,6 +167,37 @@ def test_w4a16_one_hot_rows_read_out_weight_columns_exactly(cuda_device, M):
     assert np.array_equal(out.cpu().numpy().view(np.uint16), np.ascontiguousarray(want).view(np.uint16))
 
 
+@pytest.mark.parametrize("variant", ["ring", "stream"])
+@pytest.mark.parametrize("M,N,K", [(1, 128, 128), (2, 256, 384), (8, 1024, 4096), (9, 384, 640), (16, 1792, 4096), (5, 128, 8192),
+                                   (16, 128, 4608), (12, 256, 8192)])
+def test_w4a16_decode_kernels_match_oracle(cuda_device, monkeypatch, variant, M, N, K):
+    """Both decode-sized kernels (TMA ring per warp; register-staged stream) against the oracle: K that is and is
+    not a multiple of the ring's 256-wide box, K beyond what fits in shared memory (falls back to the stream
+    kernel by itself), several units per warp (N = 1792 x 8 rows over 148 CTAs needs 13 warps)."""
+    monkeypatch.setenv("TB200_GEMV_VARIANT", variant)
+    got, want = w4_case(M, N, K, seed=300 + M + K, device=cuda_device)
+    np.testing.assert_allclose(got, want, **FP16_TOL)
+
+
+def test_w4a16_decode_ring_is_deterministic_and_exact_on_one_hot_rows(cuda_device, monkeypatch):
+    from tilebench_b200.benchmarks.operators.gemm_w4a16 import impl_cuda
+    monkeypatch.setenv("TB200_GEMV_VARIANT", "ring")
+    N, K, M = 14336, 4096, 16
+    wp, sc = tensors.make_int4_group_weights(N, K, 128, seed=31)
+    ks = torch.randperm(K, generator=torch.Generator().manual_seed(2))[:M]
+    a = torch.zeros(M, K, dtype=torch.float16)
+    a[torch.arange(M), ks] = 1.0
+    native.clear_device_status()
+    ad, wpd, scd = a.to(cuda_device), wp.to(cuda_device), sc.to(cuda_device)
+    out = impl_cuda.run(ad, wpd, scd, 128, 8)
+    again = impl_cuda.run(ad, wpd, scd, 128, 8)
+    torch.cuda.synchronize()
+    status_clean()
+    w = ref_ops.dequant_int4_group(wp.numpy(), sc.numpy(), 128, 8)
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), np.ascontiguousarray(w[:, ks.numpy()].T).view(np.uint16))
+    assert torch.equal(out, again)
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 24, 64, 127, 128, 129, 300])
 def test_w4a16_matches_oracle_across_m(cuda_device, M):
     got, want = w4_case(M, 512, 1024, seed=40 + M, device=cuda_device)

@@ -89,6 +89,7 @@ def run_benchmark_suite(operator_name, benchmark_overrides=None, enabled_backend
     use_cuda_graph = bool(bench_cfg.get("use_cuda_graph", False))
     flush = bool(bench_cfg.get("flush_l2", False))
     cpu_baseline = bool(bench_cfg.get("cpu_baseline", False))
+    timer_kind = str(bench_cfg.get("timer", "events"))
     verify_atol, verify_rtol = config_tolerance(config.get("verify", {}), detect_arch() if HAS_CUDA else None)
     timing = timing_mode(use_cuda_graph) if HAS_CUDA else None
 
@@ -103,7 +104,7 @@ def run_benchmark_suite(operator_name, benchmark_overrides=None, enabled_backend
 
     def _bench(fn, args, kw=None):
         return report_benchmark(fn, args, kwargs=kw or {}, warmup=warmup, repeat=repeat,
-                                use_cuda_graph=use_cuda_graph, flush_l2=flush)
+                                use_cuda_graph=use_cuda_graph, flush_l2=flush, timer=timer_kind)
 
     results = []
     for case_idx, case in enumerate(cases):

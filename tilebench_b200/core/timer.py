@@ -24,6 +24,15 @@ DEFAULT_WARMUP = 1
 DEFAULT_REPEAT = 3
 
 _flush_buf: torch.Tensor | None = None
+_flush_bytes_override: int | None = None
+
+
+def set_flush_bytes(nbytes: int | None) -> None:
+    """Override the size of the eviction buffer (None = 2x the last-level cache).  The reference's published B200
+    rows were taken with a fixed 64 MB buffer, half of that GPU's L2 (docs/developer_guide.md:432-433); this
+    switch reproduces that protocol for side-by-side tables."""
+    global _flush_bytes_override
+    _flush_bytes_override = int(nbytes) if nbytes else None
 
 
 def effective_use_cuda_graph(requested: bool) -> bool:
@@ -38,7 +47,9 @@ def timing_mode(requested: bool) -> dict[str, Any]:
 
 
 def flush_buffer_bytes() -> int:
-    """2x the last-level cache (B200: 2 x 126.5 MB = 253 MB)."""
+    """2x the last-level cache (B200: 2 x 126.5 MB = 253 MB), unless set_flush_bytes() overrides it."""
+    if _flush_bytes_override:
+        return _flush_bytes_override
     return 2 * (last_level_cache_bytes() or B200_L2_BYTES)
 
 
@@ -88,10 +99,31 @@ def _prepare_runner(f: Callable, args: Sequence, kwargs: dict, use_cuda_graph: b
         return (lambda: f(*args, **kwargs)), "eager", None
 
 
+def _kernel_time_ms(runner: Callable) -> float:
+    """Summed device time of the kernels `runner` launches, from the CUPTI activity records torch.profiler
+    collects — the quantity the reference's Proton-based timer reports (tilebench/core/timer.py:208-284), free
+    of launch gaps and of the cost of event records."""
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        runner()
+        torch.cuda.synchronize()
+    total_us = 0.0
+    for evt in prof.events():
+        if "memcpy" in evt.name.lower() or "memset" in evt.name.lower():
+            continue
+        total_us += float(getattr(evt, "device_time_total", 0.0) or getattr(evt, "cuda_time_total", 0.0) or 0.0)
+    if total_us <= 0.0:
+        raise RuntimeError("the profiler recorded no kernel time")
+    return total_us / 1e3
+
+
 def report_benchmark(f: Callable, args: Sequence = (), kwargs: dict | None = None, *, warmup: int = DEFAULT_WARMUP,
                      repeat: int = DEFAULT_REPEAT, use_cuda_graph: bool = False, flush_l2: bool = True,
-                     **_ignored) -> dict[str, Any]:
-    """Time `f(*args, **kwargs)`; returns {"mean", "median", "min", "max", "samples", "mode"} in ms."""
+                     timer: str = "events", **_ignored) -> dict[str, Any]:
+    """Time `f(*args, **kwargs)`; returns {"mean", "median", "min", "max", "samples", "mode", "timer"} in ms.
+    timer="events": a CUDA-event pair around the call (event-record nodes inside the graph in graph mode).
+    timer="kernel": summed kernel durations from the profiler's activity records (what Proton gives the
+    reference); falls back to events, and says so, if the profiler yields nothing."""
     kwargs = kwargs or {}
     do_flush = flush_l2
     for _ in range(max(0, warmup)):
@@ -101,6 +133,18 @@ def report_benchmark(f: Callable, args: Sequence = (), kwargs: dict | None = Non
     torch.cuda.synchronize()
     runner, mode, graph_events = _prepare_runner(f, args, kwargs, use_cuda_graph)
     samples = []
+    if timer == "kernel":
+        try:
+            for _ in range(max(1, repeat)):
+                if do_flush:
+                    flush_l2_cache()
+                torch.cuda.synchronize()
+                samples.append(_kernel_time_ms(runner))
+            return {"mean": statistics.fmean(samples), "median": statistics.median(samples), "min": min(samples),
+                    "max": max(samples), "samples": samples, "mode": mode, "timer": "kernel_time_sum"}
+        except Exception:
+            samples = []
+            torch.cuda.synchronize()
     for _ in range(max(1, repeat)):
         if do_flush:
             flush_l2_cache()
@@ -116,7 +160,7 @@ def report_benchmark(f: Callable, args: Sequence = (), kwargs: dict | None = Non
         end.synchronize()
         samples.append(start.elapsed_time(end))
     return {"mean": statistics.fmean(samples), "median": statistics.median(samples), "min": min(samples),
-            "max": max(samples), "samples": samples, "mode": mode}
+            "max": max(samples), "samples": samples, "mode": mode, "timer": "cuda_events"}
 
 
 def report_benchmark_batched(launchers: Sequence[Callable[[], Any]], *, warmup: int = 3, repeat: int = 20) -> dict[str, Any]:

@@ -27,7 +27,7 @@ INCLUDE = PKG.parent / "include"
 LIB_NAME = "libtb200.so"
 EXT_STEM = "_tb200_torch"
 
-CU_SOURCES = ["api.cu", "comm.cu", "dequant.cu", "gemm_fp8.cu", "gemm_i8.cu", "gemm_plain.cu", "gemm_w4a16.cu", "gemv_w4a16.cu", "quant.cu"]
+CU_SOURCES = ["api.cu", "comm.cu", "dequant.cu", "gemm_fp8.cu", "gemm_i8.cu", "gemm_plain.cu", "gemm_w4a16.cu", "gemv_w4a16.cu", "gemv_w4a16_ring.cu", "quant.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

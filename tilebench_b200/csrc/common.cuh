@@ -338,6 +338,11 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar, uint16_t cta_mask)
 int launch_gemv_w4a16(const void* a, const void* wp, const void* scales, void* out, int64_t m, int64_t n, int64_t k,
                       int64_t group, int zero_point, int64_t ldo, int64_t col_offset, cudaStream_t st);
 
+// TMA-ring form of the same shape (gemv_w4a16_ring.cu): taken when the activations fit in shared memory.
+bool gemv_ring_fits(int64_t m, int64_t k);
+int launch_gemv_w4a16_ring(const void* a, const void* wp, const void* scales, void* out, int64_t m, int64_t n, int64_t k,
+                           int64_t group, int zero_point, int64_t ldo, int64_t col_offset, cudaStream_t st);
+
 // ---- host: TMA descriptor encoding through the driver entry point (no libcuda link) ----------
 // 2-D row-major tensor [rows, cols] of elem_bytes-wide elements with row pitch `pitch_bytes`,
 // box [box_rows, box_cols], given swizzle.  Returns TB200_OK or an error code.

@@ -657,7 +657,15 @@ int gemm_w4a16_impl(const void* a, const void* wp, const void* scales, void* out
     if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) return fail(TB200_ERR_UNSUPPORTED, "gemm_w4a16: dimension too large");
     if (!aligned16(a) || !aligned16(wp)) return fail(TB200_ERR_ALIGN, "gemm_w4a16: a and wp must be 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (use_gemv(m, group) && peers.count == 0) return launch_gemv_w4a16(a, wp, scales, out, m, n, k, group, zero_point, ldo, col_offset, st);
+    if (use_gemv(m, group) && peers.count == 0) {
+        // decode-sized m: the TMA-ring streaming kernel when the activations fit beside the rings in shared
+        // memory, else the register-staged one (TB200_GEMV_VARIANT=stream forces the latter; tests compare both)
+        const char* knob = getenv("TB200_GEMV_VARIANT");
+        const bool want_stream = knob && knob[0] == 's';
+        if (!want_stream && gemv_ring_fits(m, k))
+            return launch_gemv_w4a16_ring(a, wp, scales, out, m, n, k, group, zero_point, ldo, col_offset, st);
+        return launch_gemv_w4a16(a, wp, scales, out, m, n, k, group, zero_point, ldo, col_offset, st);
+    }
     const int splitk = pick_splitk(m, n, k);
     float* ws = nullptr;
     if (splitk > 1) {

@@ -63,6 +63,8 @@ def build_overrides(args) -> dict:
         ov["cpu_baseline"] = True
     if args.seed is not None:
         ov["seed"] = args.seed
+    if args.timer:
+        ov["timer"] = args.timer
     if args.case_indices:
         ov["case_indices"] = [int(x) for x in args.case_indices.split(",") if x.strip()]
     return ov
@@ -109,6 +111,10 @@ def main(argv=None) -> int:
     ap.add_argument("--autotune", action="store_true", help="kept for layout parity: the cuda backend has a static config table")
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--no-flush-l2", action="store_true")
+    ap.add_argument("--flush-mb", type=float, default=None,
+                    help="size of the L2 eviction buffer in MB (default: 2x L2; 64 reproduces the reference's published B200 protocol)")
+    ap.add_argument("--timer", choices=["events", "kernel"], default=None,
+                    help="events: CUDA-event pair (default); kernel: summed kernel durations from the profiler, as the reference's Proton timer reports")
     ap.add_argument("--cpu-baseline", action="store_true", help="also time the PyTorch reference on the host CPU cores")
     ap.add_argument("--case-indices", default=None)
     ap.add_argument("--seed", type=int)
@@ -116,9 +122,13 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
 
     from tilebench_b200.core.engine import run_benchmark_suite
+    if args.flush_mb:
+        from tilebench_b200.core import timer
+        timer.set_flush_bytes(int(args.flush_mb * (1 << 20)))
     active = parse_backends(args.tile_language)
     mode = MODES[1] if args.autotune else MODES[0]
     prov = provenance.collect(args.gpu)
+    prov["flush_mb"] = args.flush_mb
     results = run_benchmark_suite(args.operator, build_overrides(args), active)
     if not results:
         print("No case produced a result; existing logs are left untouched.", file=sys.stderr)
