@@ -91,7 +91,7 @@ def run_benchmark_suite(operator_name, benchmark_overrides=None, enabled_backend
     cpu_baseline = bool(bench_cfg.get("cpu_baseline", False))
     timer_kind = str(bench_cfg.get("timer", "events"))
     verify_atol, verify_rtol = config_tolerance(config.get("verify", {}), detect_arch() if HAS_CUDA else None)
-    timing = timing_mode(use_cuda_graph) if HAS_CUDA else None
+    timing = timing_mode(use_cuda_graph, str(bench_cfg.get("timer", "events"))) if HAS_CUDA else None
 
     cases = expand_cases(operator_name, config)
     case_indices = bench_cfg.get("case_indices")

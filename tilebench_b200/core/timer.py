@@ -39,11 +39,11 @@ def effective_use_cuda_graph(requested: bool) -> bool:
     return bool(requested)
 
 
-def timing_mode(requested: bool) -> dict[str, Any]:
+def timing_mode(requested: bool, timer: str = "events") -> dict[str, Any]:
     eff = effective_use_cuda_graph(requested)
     return {"requested_use_cuda_graph": bool(requested), "effective_use_cuda_graph": eff,
             "timing_execution_mode": "graph" if eff else "eager", "timing_note": None,
-            "timer": "cuda_events"}
+            "timer": "kernel_time_sum" if timer == "kernel" else "cuda_events"}
 
 
 def flush_buffer_bytes() -> int:

@@ -14,18 +14,29 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
 
-// Persistent launch: at most one full wave of CTAs (every SM's thread slots), and — when the work
-// needs several passes — a grid that gives every CTA the same number of passes, so no SM idles
-// while a few CTAs run one pass more.
+// Launch shape of the streaming kernels: a grid that gives every CTA the same number of passes, sized against the
+// SM's thread slots rather than against what is resident at once.  (Measured: capping the grid at the kernel's
+// real occupancy — two CTAs per SM for the deep-unroll kernels — so that a single resident wave loops over all
+// passes took the headline from 6.24 to 5.60 TB/s; the hardware's CTA scheduler refilling SMs as CTAs retire
+// spreads the tail better than a fixed assignment does.)
 inline unsigned grid_for(uint64_t work_items, int threads, int unroll) {
     uint64_t per_cta = static_cast<uint64_t>(threads) * unroll;
     uint64_t need = (work_items + per_cta - 1) / per_cta;
-    uint64_t cap = static_cast<uint64_t>(num_sms()) * (2048 / threads);
+    uint64_t sms = static_cast<uint64_t>(num_sms());
+    uint64_t cap = sms * (2048 / threads);
     if (need < 1) need = 1;
+    if (need < 4 * sms) {
+        // small inputs: spread the items over more CTAs (up to four per SM) instead of unrolling inside few of them;
+        // the kernels skip the unroll steps that fall beyond the end, so any grid is valid
+        uint64_t one_each = (work_items + threads - 1) / threads;
+        uint64_t spread = one_each < 4 * sms ? one_each : 4 * sms;
+        return static_cast<unsigned>(spread > need ? spread : need);
+    }
     if (need <= cap) return static_cast<unsigned>(need);
     uint64_t passes = (need + cap - 1) / cap;
     return static_cast<unsigned>((need + passes - 1) / passes);
 }
+#define TB200_GRID_FOR(kern, work, threads, unroll) grid_for(work, threads, unroll)
 
 // Two nibbles of one byte -> half2 (low nibble first), exact:  h = 0x6400 | q  is 1024 + q.
 __device__ __forceinline__ __half2 nib_pair_to_half2(uint32_t lo_src, uint32_t hi_src, uint32_t sel) {
@@ -355,13 +366,12 @@ template <> struct Vec16<TB200_DT_F16> {
     __device__ static float load_scale(const void* s, uint64_t i) {
         return __half2float(__ldg(reinterpret_cast<const __half*>(s) + i));
     }
+    // one HMUL2 per two elements: a correctly rounded fp16 product, i.e. the exact fp32 product rounded once
     __device__ static uint4 mul(uint4 x, float s) {
         __half2* h = reinterpret_cast<__half2*>(&x);
+        const __half2 s2 = __float2half2_rn(s);                 // s came from an fp16 value: exact
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float2 f = __half22float2(h[i]);
-            h[i] = __floats2half2_rn(__fmul_rn(f.x, s), __fmul_rn(f.y, s));
-        }
+        for (int i = 0; i < 4; ++i) h[i] = __hmul2(h[i], s2);
         return x;
     }
 };
@@ -370,13 +380,12 @@ template <> struct Vec16<TB200_DT_BF16> {
     __device__ static float load_scale(const void* s, uint64_t i) {
         return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(s) + i));
     }
+    // one bf16x2 multiply per two elements (correctly rounded: the exact fp32 product rounded once)
     __device__ static uint4 mul(uint4 x, float s) {
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&x);
+        const __nv_bfloat162 s2 = __float2bfloat162_rn(s);      // s came from a bf16 value: exact
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float2 f = __bfloat1622float2(h[i]);
-            h[i] = __floats2bfloat162_rn(__fmul_rn(f.x, s), __fmul_rn(f.y, s));
-        }
+        for (int i = 0; i < 4; ++i) h[i] = __hmul2(h[i], s2);
         return x;
     }
 };
@@ -518,20 +527,20 @@ extern "C" int tb200_dequant_int4_group(const void* wp, const void* scales, void
                       aligned16(wp) && (k / 32 < (1ll << 32));
     if (wide) {
         const uint64_t total = static_cast<uint64_t>(n) * static_cast<uint64_t>(k / 32);
-        const unsigned grid = grid_for(total, kThreads, kWideUnroll4);
+        const unsigned grid = TB200_GRID_FOR(tb200_k_dequant_int4_group_wide, total, kThreads, kWideUnroll4);
         tb200_k_dequant_int4_group_wide<<<grid, kThreads, 0, st>>>(
             static_cast<const uint4*>(wp), static_cast<const __half*>(scales), static_cast<__half*>(out),
             static_cast<uint32_t>(k / 32), static_cast<uint32_t>(group / 32), static_cast<uint32_t>(k / group), total,
             ldo, 1024.0f + static_cast<float>(zero_point));
     } else if (vec) {
         uint64_t total = static_cast<uint64_t>(n) * static_cast<uint64_t>(k / 8);
-        unsigned grid = grid_for(total, kThreads, kUnroll);
+        unsigned grid = TB200_GRID_FOR(tb200_k_dequant_int4_group, total, kThreads, kUnroll);
         tb200_k_dequant_int4_group<<<grid, kThreads, 0, st>>>(
             static_cast<const uint32_t*>(wp), static_cast<const __half*>(scales), static_cast<__half*>(out),
             static_cast<uint32_t>(k / 8), static_cast<uint32_t>(group / 8), static_cast<uint32_t>(k / group), total,
             ldo, 1024.0f + static_cast<float>(zero_point));
     } else {
-        unsigned grid = grid_for(static_cast<uint64_t>(n) * k, kThreads, 1);
+        unsigned grid = TB200_GRID_FOR(tb200_k_dequant_int4_group_scalar, static_cast<uint64_t>(n) * k, kThreads, 1);
         tb200_k_dequant_int4_group_scalar<<<grid, kThreads, 0, st>>>(
             static_cast<const uint8_t*>(wp), static_cast<const __half*>(scales), static_cast<__half*>(out), n, k,
             group, zero_point, ldo);
@@ -559,22 +568,22 @@ extern "C" int tb200_dequant_int8_rowwise(const void* w, const float* scale, voi
     if (wide && wide_total >= sms * kThreads * 2) {
         // deep variant once it still gives every SM two CTAs, else two chunks per thread
         const bool deep = wide_total >= 2 * sms * kThreads * kWideUnroll;
-        const unsigned grid = grid_for(wide_total, kThreads, deep ? kWideUnroll : 2);
         auto kern = deep ? (bf16 ? (use_post ? tb200_k_dequant_int8_rowwise_bf16_post_wide : tb200_k_dequant_int8_rowwise_bf16_wide)
                                  : (use_post ? tb200_k_dequant_int8_rowwise_f16_post_wide : tb200_k_dequant_int8_rowwise_f16_wide))
                          : (bf16 ? (use_post ? tb200_k_dequant_int8_rowwise_bf16_post_wide2 : tb200_k_dequant_int8_rowwise_bf16_wide2)
                                  : (use_post ? tb200_k_dequant_int8_rowwise_f16_post_wide2 : tb200_k_dequant_int8_rowwise_f16_wide2));
+        const unsigned grid = TB200_GRID_FOR(kern, wide_total, kThreads, deep ? kWideUnroll : 2);
         kern<<<grid, kThreads, 0, st>>>(static_cast<const uint8_t*>(w), scale, static_cast<uint8_t*>(out),
                                         static_cast<uint32_t>(cols / 32), wide_total, post);
     } else if (vec) {
         uint64_t total = static_cast<uint64_t>(rows) * static_cast<uint64_t>(cols / 8);
-        unsigned grid = grid_for(total, kThreads, kUnroll);
         auto kern = bf16 ? (use_post ? tb200_k_dequant_int8_rowwise_bf16_post : tb200_k_dequant_int8_rowwise_bf16)
                          : (use_post ? tb200_k_dequant_int8_rowwise_f16_post : tb200_k_dequant_int8_rowwise_f16);
+        unsigned grid = TB200_GRID_FOR(kern, total, kThreads, kUnroll);
         kern<<<grid, kThreads, 0, st>>>(static_cast<const uint2*>(w), scale, static_cast<uint4*>(out),
                                         static_cast<uint32_t>(cols / 8), total, post);
     } else {
-        unsigned grid = grid_for(static_cast<uint64_t>(rows) * cols, kThreads, 1);
+        unsigned grid = TB200_GRID_FOR(tb200_k_dequant_int8_rowwise_scalar, static_cast<uint64_t>(rows) * cols, kThreads, 1);
         tb200_k_dequant_int8_rowwise_scalar<<<grid, kThreads, 0, st>>>(static_cast<const int8_t*>(w), scale, out,
                                                                        rows, cols, bf16 ? 1 : 0, use_post, post);
     }
@@ -602,24 +611,24 @@ extern "C" int tb200_weight_dequant_block(const void* x, const void* s, void* y,
     const uint64_t sms = static_cast<uint64_t>(num_sms());
     if (wide && wide_total >= sms * kThreads * 2) {
         const bool deep = wide_total >= 2 * sms * kThreads * kWideUnroll;
-        const unsigned grid = grid_for(wide_total, kThreads, deep ? kWideUnroll : 2);
         auto kern = deep ? (dtype == TB200_DT_F32 ? tb200_k_weight_dequant_f32_wide
                             : dtype == TB200_DT_F16 ? tb200_k_weight_dequant_f16_wide : tb200_k_weight_dequant_bf16_wide)
                          : (dtype == TB200_DT_F32 ? tb200_k_weight_dequant_f32_wide2
                             : dtype == TB200_DT_F16 ? tb200_k_weight_dequant_f16_wide2 : tb200_k_weight_dequant_bf16_wide2);
+        const unsigned grid = TB200_GRID_FOR(kern, wide_total, kThreads, deep ? kWideUnroll : 2);
         kern<<<grid, kThreads, 0, st>>>(static_cast<const uint8_t*>(x), s, static_cast<uint8_t*>(y),
                                         static_cast<uint32_t>(n / (2 * elems)), static_cast<uint32_t>(tile / (2 * elems)),
                                         static_cast<uint32_t>(tile), static_cast<uint32_t>(s_cols), wide_total);
     } else if (vec) {
         uint64_t total = static_cast<uint64_t>(m) * static_cast<uint64_t>(n / elems);
-        unsigned grid = grid_for(total, kThreads, kUnroll);
         auto kern = dtype == TB200_DT_F32 ? tb200_k_weight_dequant_f32
                     : dtype == TB200_DT_F16 ? tb200_k_weight_dequant_f16 : tb200_k_weight_dequant_bf16;
+        unsigned grid = TB200_GRID_FOR(kern, total, kThreads, kUnroll);
         kern<<<grid, kThreads, 0, st>>>(static_cast<const uint4*>(x), s, static_cast<uint4*>(y),
                                         static_cast<uint32_t>(n / elems), static_cast<uint32_t>(tile / elems),
                                         static_cast<uint32_t>(tile), static_cast<uint32_t>(s_cols), total);
     } else {
-        unsigned grid = grid_for(static_cast<uint64_t>(m) * n, kThreads, 1);
+        unsigned grid = TB200_GRID_FOR(tb200_k_weight_dequant_scalar, static_cast<uint64_t>(m) * n, kThreads, 1);
         tb200_k_weight_dequant_scalar<<<grid, kThreads, 0, st>>>(x, s, y, m, n, tile, s_cols, dtype);
     }
     TB200_CUDA_TRY(cudaGetLastError());
