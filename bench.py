@@ -92,7 +92,7 @@ def fill_tensor_fractions(rows, peaks):
     return rows
 
 
-def add_live_peaks(peaks, kinds=("fp8_e4m3fn", "int8", "tf32"), sustained_s=1.5):
+def add_live_peaks(peaks, kinds=("fp8_e4m3fn", "int8", "tf32"), sustained_s=1.5, live=True):
     """The tensor-core denominators the driver's file lacks, measured now on this GPU with the library GEMMs
     (tilebench_b200.measure_peak: torch._scaled_mm e4m3, torch._int_mm, TF32 matmul; burst and a short loop).
     A kind that cannot be measured falls back to the block committed in data/peak_performance/B200.json."""
@@ -101,6 +101,8 @@ def add_live_peaks(peaks, kinds=("fp8_e4m3fn", "int8", "tf32"), sustained_s=1.5)
     committed = (load_peak_config("B200").get("measured") or {})
     for kind in kinds:
         try:
+            if not live:
+                raise RuntimeError("live probe switched off")
             r = measure_peak.measure_gemm(kind, 8192, sustained_s=sustained_s)
             peaks["tflops"][kind] = {"burst": r["tflops"], "sustained": r["tflops_sustained"],
                                      "source": f"library GEMM 8192^3 measured in this run ({kind})"}
@@ -108,7 +110,7 @@ def add_live_peaks(peaks, kinds=("fp8_e4m3fn", "int8", "tf32"), sustained_s=1.5)
             burst = (committed.get("tflops") or {}).get(kind)
             if burst:
                 peaks["tflops"][kind] = {"burst": burst, "sustained": (committed.get("tflops_sustained") or {}).get(kind, burst),
-                                         "source": f"committed measure_peak block (live probe failed: {type(e).__name__})"}
+                                         "source": f"committed measure_peak block ({e})"}
     return peaks
 
 
@@ -541,7 +543,7 @@ def run_ours(args):
         torch.cuda.empty_cache()
         try:
             extra = sections(torch, dev, peaks, world, rank, args.steps, args.warmup)
-            add_live_peaks(peaks)               # after the sections, so the probes' seconds-long loops do not pre-heat them
+            add_live_peaks(peaks, live=not args.no_live_peaks)    # after the sections, so the probes' seconds-long loops do not pre-heat them
             fill_tensor_fractions(extra, peaks)
         except Exception as e:  # a failing section must not lose the headline
             extra = [{"name": "sections", "error": f"{type(e).__name__}: {e}"}]
@@ -601,6 +603,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--sections", choices=["all", "multi", "none"], default="all",
                     help="all: every section; multi: headline + the multi_gpu section only (N > 1); none: headline only")
+    ap.add_argument("--no-live-peaks", action="store_true",
+                    help="skip the seconds-long library-GEMM probes (profiler runs); fractions then use the committed measure_peak block")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     args.out = _own_stdout()

@@ -98,7 +98,10 @@ def test_metrics_formulas_for_the_configs():
     d = metrics.compute_derived(row, cfg, peak)["cuda"]
     assert math.isclose(d["bandwidth_GBs"], 42_205_184 / 0.01e-3 / 1e9)
     assert math.isclose(d["pct_peak_bw"], d["bandwidth_GBs"] / 6539.4 * 100)
-    assert math.isclose(d["pct_measured_bw"], d["bandwidth_GBs"] / 6550.7 * 100)
+    assert math.isclose(d["pct_measured_bw"], d["bandwidth_GBs"] / peak["measured"]["hbm_GBs"] * 100)
+    # every tensor-core input type of the path has a measured denominator (burst and sustained)
+    for kind in ("fp16", "bf16", "tf32", "fp8_e4m3fn", "int8"):
+        assert peak["measured"]["tflops"][kind] > peak["measured"]["tflops_sustained"][kind] > 0
     assert math.isclose(d["speedup"], 20.0)
     cfg = yaml.safe_load(open(operator_config("dequant_int8_channel")))["metrics"]
     for rows, nbytes in ((256, 3_146_752), (4096, 50_348_032), (65536, 805_568_512)):
