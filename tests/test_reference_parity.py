@@ -1,9 +1,9 @@
 """The harness functions this package restates — case-grid expansion, verifier, tolerance lookup, derived
 metrics — against the reference's OWN functions, on this package's operator configs.
 
-Runs only where a TileBench checkout can be imported (TILEBENCH_REFERENCE=/path/to/checkout, or the default
-location below); elsewhere — e.g. on a GPU box that only carries this repository — it is skipped, and the
-committed fixtures under tests/golden/ are what ties the package to reference code."""
+Runs only where a TileBench checkout can be imported (TILEBENCH_REFERENCE=/path/to/checkout, or a `reference`
+folder beside this repository); elsewhere — e.g. on a GPU box that only carries this repository — it is skipped,
+and the committed fixtures under tests/golden/ are what ties the package to reference code."""
 import importlib
 import math
 import os
@@ -18,7 +18,7 @@ from tilebench_b200.core import metrics, verifier
 from tilebench_b200.data import tensors
 from tilebench_b200.paths import list_operators, operator_config
 
-REF_ROOT = Path(os.environ.get("TILEBENCH_REFERENCE", "/root/reference"))
+REF_ROOT = Path(os.environ.get("TILEBENCH_REFERENCE") or Path(__file__).resolve().parents[2] / "reference")
 
 
 @pytest.fixture(scope="module")
