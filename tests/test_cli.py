@@ -28,8 +28,8 @@ def test_cli_writes_timing_provenance_and_csv(monkeypatch, tmp_path, capsys):
     assert rc == 0
     assert calls["op"] == "dequant_int4_group" and calls["backends"] == ["cuda"]
     assert calls["overrides"] == {"warmup": 2, "repeat": 5, "cpu_baseline": True, "case_indices": [0]}
-    timing = tmp_path / "B200" / "logs" / "dequant_int4_group_default_cuda_timing.json"
-    prov = tmp_path / "B200" / "logs" / "dequant_int4_group_default_cuda_provenance.json"
+    timing = tmp_path / "B200" / "logs" / "time_measurement_logs" / "dequant_int4_group_default_cuda.json"
+    prov = tmp_path / "B200" / "logs" / "provenance" / "dequant_int4_group_default_cuda.json"
     rows = json.loads(timing.read_text())
     assert rows[0]["derived"]["cuda"]["bandwidth_GBs"] == pytest.approx(42_205_184 / 0.01e-3 / 1e9)
     assert json.loads(prov.read_text())["device"]["requested_label"] == "B200"
@@ -37,6 +37,8 @@ def test_cli_writes_timing_provenance_and_csv(monkeypatch, tmp_path, capsys):
     assert table[0][:5] == ["params", "dtype", "torch_ms", "cuda_ms", "speedup_cuda"]
     assert table[1][0] == "GROUP=128, K=4096, N=4096, ZP=8" and table[1][2:5] == ["0.2000", "0.0100", "20.00"]
     assert float(table[1][table[0].index("cuda_pct_measured_bw")]) == pytest.approx(4220.5184 / 6550.7 * 100, rel=1e-3)
+    assert run_bench.timing_log_path("B200", "dequant_int4_group", "default", ["cuda"]).parts[-4:] == \
+        ("B200", "logs", "time_measurement_logs", "dequant_int4_group_default_cuda.json")
     assert "Summary CSV" in capsys.readouterr().out
 
 

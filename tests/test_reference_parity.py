@@ -27,7 +27,8 @@ def ref():
         pytest.skip(f"no TileBench checkout at {REF_ROOT}")
     sys.path.insert(0, str(REF_ROOT))
     try:
-        mods = {name: importlib.import_module(f"tilebench.{name}") for name in ("core.verifier", "core.metrics", "data.tensors", "core.dtypes")}
+        mods = {name: importlib.import_module(f"tilebench.{name}")
+                for name in ("core.verifier", "core.metrics", "data.tensors", "core.dtypes", "paths", "backends")}
     except Exception as e:          # a checkout whose dependencies are missing here
         pytest.skip(f"reference not importable: {type(e).__name__}: {e}")
     finally:
@@ -106,3 +107,30 @@ def test_compute_derived_equals_the_reference(ref):
     from tilebench_b200.core.dtypes import dtype_size
     for name in ("fp32", "fp16", "bf16", "fp8_e4m3fn", "int8", "int32", "unknown"):
         assert dtype_size(name) == ref["core.dtypes"].dtype_size(name), name
+
+
+def test_result_layout_is_where_the_reference_tools_look(ref, monkeypatch, tmp_path):
+    """A run of this package's CLI writes its timing log under the name and folder the reference's path helpers give
+    for a backend selection of ("cuda",) once `cuda` is a registered backend there, and the rows in it are read by the
+    reference's compute_derived — i.e. the reference's plotting script finds and understands them."""
+    import json
+    import tilebench_b200.core.engine as engine
+    from tilebench_b200 import run_bench
+    rb, rp, rm = ref["backends"], ref["paths"], ref["core.metrics"]
+    monkeypatch.setattr(rb, "BACKEND_ORDER", tuple(rb.BACKEND_ORDER) + ("cuda",))        # the one-line edit a checkout makes
+    monkeypatch.setattr(rm, "BACKENDS", tuple(rm.BACKENDS) + ("cuda",))
+    row = {"params": {"rows": 4096, "cols": 4096}, "problem_size": 4096 * 4096, "dtype": "bf16", "seed": 1, "torch_ms": 0.1,
+           "torch_stats": {"mean": 0.1}, "cuda_ms": 0.01, "cuda_stats": {"mean": 0.01}, "cuda_ok": True, "cuda_err": "",
+           "cuda_autotune_cfg": None, "speedup_cuda": 10.0, "timing": None}
+    monkeypatch.setattr(engine, "run_benchmark_suite", lambda *a, **k: [dict(row)])
+    assert run_bench.main(["--operator", "dequant_int8_channel", "--output-root", str(tmp_path)]) == 0
+    theirs = rp.timing_log_path("B200", "dequant_int8_channel", "default", ["cuda"])
+    mine = tmp_path / "B200" / "logs" / "time_measurement_logs" / "dequant_int8_channel_default_cuda.json"
+    assert mine.is_file() and theirs.parts[-3:] == mine.parts[-3:]
+    assert rp.provenance_log_path("B200", "dequant_int8_channel", "default", ["cuda"]).parts[-3:] == \
+        (tmp_path / "B200" / "logs" / "provenance" / "dequant_int8_channel_default_cuda.json").parts[-3:]
+    rows = json.loads(mine.read_text())
+    cfg = yaml.safe_load(open(operator_config("dequant_int8_channel")))["metrics"]
+    derived = rm.compute_derived(rows[0], cfg, rm.load_peak_config("B200"))
+    assert derived["cuda"]["bandwidth_GBs"] == pytest.approx(rows[0]["derived"]["cuda"]["bandwidth_GBs"])
+    assert derived["cuda"]["speedup"] == pytest.approx(10.0)

@@ -3,8 +3,10 @@
     python -m tilebench_b200.run_bench --gpu B200 --operator dequant_int4_group
     python -m tilebench_b200.run_bench --gpu B200 --operator gemm_w4a16 --case-indices 0,3 --cpu-baseline
 
-Same surface and result layout as the reference CLI (scripts/run_bench.py:199-447): a timing JSON and a
-provenance sidecar under results/<gpu>/logs/, a summary CSV under results/<gpu>/csv/<op>_<mode>.csv with
+Same surface and result layout as the reference CLI (scripts/run_bench.py:199-447, tilebench/paths.py:111-136):
+the raw timing JSON at results/<gpu>/logs/time_measurement_logs/<op>_<mode>_<backends>.json (where the reference's
+scripts/visualize.py looks for it), the provenance sidecar under the same name in results/<gpu>/logs/provenance/,
+a summary CSV at results/<gpu>/csv/<op>_<mode>.csv with
 `params, dtype, torch_ms, cuda_ms, speedup_cuda`, extended here by the derived columns the north star
 asks for (GB/s or TFLOPS and the fraction of the HBM / tensor roofline, against the datasheet table and
 against the peaks measured on the box).  An empty result set never overwrites existing logs.
@@ -29,8 +31,19 @@ _BACKEND_LABEL = {"cuda": "CUDA"}
 _SPEEDUP_CODE = {"cuda": "cu"}
 
 
+def log_name(operator: str, mode: str, backends) -> str:
+    """<operator>_<mode>_<backend tag>.json: one name for the timing log and its provenance sidecar."""
+    if mode not in MODES:
+        raise ValueError(f"unknown mode {mode!r}; choose from {', '.join(MODES)}")
+    return f"{operator}_{mode}_{backend_tag(backends)}.json"
+
+
 def timing_log_path(gpu: str, operator: str, mode: str, backends) -> Path:
-    return results_logs_dir(gpu) / f"{operator}_{mode}_{backend_tag(backends)}_timing.json"
+    return results_logs_dir(gpu) / "time_measurement_logs" / log_name(operator, mode, backends)
+
+
+def provenance_log_path(gpu: str, operator: str, mode: str, backends) -> Path:
+    return results_logs_dir(gpu) / "provenance" / log_name(operator, mode, backends)
 
 
 def fmt_params(row: dict) -> str:
@@ -76,10 +89,10 @@ def write_outputs(gpu: str, operator: str, mode: str, active, results, prov, out
     peak = load_peak_config(gpu)
     logs = (out_root / gpu / "logs") if out_root else results_logs_dir(gpu)
     csvd = (out_root / gpu / "csv") if out_root else results_csv_dir(gpu)
-    logs.mkdir(parents=True, exist_ok=True)
-    csvd.mkdir(parents=True, exist_ok=True)
-    timing = logs / timing_log_path(gpu, operator, mode, active).name
-    sidecar = timing.with_name(timing.stem.replace("_timing", "") + "_provenance.json")
+    timing = logs / "time_measurement_logs" / log_name(operator, mode, active)
+    sidecar = logs / "provenance" / log_name(operator, mode, active)
+    for d in (timing.parent, sidecar.parent, csvd):
+        d.mkdir(parents=True, exist_ok=True)
     csv_path = csvd / f"{operator}_{mode}.csv"
     for r in results:
         r["derived"] = compute_derived(r, metrics_cfg, peak)
