@@ -353,7 +353,10 @@ namespace {
 template <int DT> struct Vec16;  // 16-byte chunk traits
 template <> struct Vec16<TB200_DT_F32> {
     static constexpr int kElems = 4;
-    __device__ static float load_scale(const void* s, uint64_t i) { return __ldg(reinterpret_cast<const float*>(s) + i); }
+    // load_raw / scale: the load is issued with nothing depending on it, the conversion happens where the value is
+    // used — a dependent instruction right behind the load would hold back the data loads queued after it
+    __device__ static uint32_t load_raw(const void* s, uint64_t i) { return __float_as_uint(__ldg(reinterpret_cast<const float*>(s) + i)); }
+    __device__ static float scale(uint32_t raw) { return __uint_as_float(raw); }
     __device__ static uint4 mul(uint4 x, float s) {
         float* f = reinterpret_cast<float*>(&x);
 #pragma unroll
@@ -363,9 +366,8 @@ template <> struct Vec16<TB200_DT_F32> {
 };
 template <> struct Vec16<TB200_DT_F16> {
     static constexpr int kElems = 8;
-    __device__ static float load_scale(const void* s, uint64_t i) {
-        return __half2float(__ldg(reinterpret_cast<const __half*>(s) + i));
-    }
+    __device__ static uint32_t load_raw(const void* s, uint64_t i) { return __ldg(reinterpret_cast<const unsigned short*>(s) + i); }
+    __device__ static float scale(uint32_t raw) { return __half2float(__ushort_as_half(static_cast<unsigned short>(raw))); }
     // one HMUL2 per two elements: a correctly rounded fp16 product, i.e. the exact fp32 product rounded once
     __device__ static uint4 mul(uint4 x, float s) {
         __half2* h = reinterpret_cast<__half2*>(&x);
@@ -377,9 +379,8 @@ template <> struct Vec16<TB200_DT_F16> {
 };
 template <> struct Vec16<TB200_DT_BF16> {
     static constexpr int kElems = 8;
-    __device__ static float load_scale(const void* s, uint64_t i) {
-        return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(s) + i));
-    }
+    __device__ static uint32_t load_raw(const void* s, uint64_t i) { return __ldg(reinterpret_cast<const unsigned short*>(s) + i); }
+    __device__ static float scale(uint32_t raw) { return __uint_as_float(raw << 16); }      // bf16 -> fp32 is a 16-bit shift
     // one bf16x2 multiply per two elements (correctly rounded: the exact fp32 product rounded once)
     __device__ static uint4 mul(uint4 x, float s) {
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&x);
@@ -399,7 +400,7 @@ __device__ __forceinline__ void weight_dequant_body(const uint4* __restrict__ x,
     for (uint64_t base = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; base < total_chunks;
          base += stride * kUnroll) {
         uint4 raw[kUnroll];
-        float sc[kUnroll];
+        uint32_t sc[kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             uint64_t c = base + u * stride;
@@ -407,13 +408,13 @@ __device__ __forceinline__ void weight_dequant_body(const uint4* __restrict__ x,
                 uint64_t row = c / chunks_per_row;
                 uint32_t cc = static_cast<uint32_t>(c - row * chunks_per_row);
                 raw[u] = __ldg(x + c);
-                sc[u] = Vec16<DT>::load_scale(s, (row / tile_rows) * s_cols + cc / tile_chunks);
+                sc[u] = Vec16<DT>::load_raw(s, (row / tile_rows) * s_cols + cc / tile_chunks);
             }
         }
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             uint64_t c = base + u * stride;
-            if (c < total_chunks) y[c] = Vec16<DT>::mul(raw[u], sc[u]);
+            if (c < total_chunks) y[c] = Vec16<DT>::mul(raw[u], Vec16<DT>::scale(sc[u]));
         }
     }
 }
@@ -429,7 +430,7 @@ __device__ __forceinline__ void weight_dequant_wide_body(const uint8_t* __restri
     for (uint64_t base = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; base < total_chunks;
          base += stride * U) {
         uint32_t raw[U][8];
-        float sc[U];
+        uint32_t sc[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const uint64_t c = base + u * stride;
@@ -437,15 +438,16 @@ __device__ __forceinline__ void weight_dequant_wide_body(const uint8_t* __restri
                 const uint64_t row = c / chunks_per_row;
                 const uint32_t cc = static_cast<uint32_t>(c - row * chunks_per_row);
                 ldg256(x + c * 32, raw[u]);
-                sc[u] = Vec16<DT>::load_scale(s, (row / tile_rows) * s_cols + cc / tile_chunks);
+                sc[u] = Vec16<DT>::load_raw(s, (row / tile_rows) * s_cols + cc / tile_chunks);
             }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const uint64_t c = base + u * stride;
             if (c < total_chunks) {
-                const uint4 lo = Vec16<DT>::mul(make_uint4(raw[u][0], raw[u][1], raw[u][2], raw[u][3]), sc[u]);
-                const uint4 hi = Vec16<DT>::mul(make_uint4(raw[u][4], raw[u][5], raw[u][6], raw[u][7]), sc[u]);
+                const float scale = Vec16<DT>::scale(sc[u]);
+                const uint4 lo = Vec16<DT>::mul(make_uint4(raw[u][0], raw[u][1], raw[u][2], raw[u][3]), scale);
+                const uint4 hi = Vec16<DT>::mul(make_uint4(raw[u][4], raw[u][5], raw[u][6], raw[u][7]), scale);
                 const uint32_t o[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
                 stg256(y + c * 32, o);
             }

@@ -206,7 +206,7 @@ __device__ __forceinline__ void gemv_ring_body(const CUtensorMap* __restrict__ t
         // running group index of the next 128-wide block whose scales are fetched (two blocks per box)
         int fg = fg0, fin = fin0;
         auto next_scales = [&](__half& lo, __half& hi) {
-            lo = __ldg(srow + fg);
+            lo = __ldg(srow + fg);                               // plain loads: nothing may depend on them before their use
             hi = __ldg(srow + hi_row + fg);
             if (++fin == group128) { fin = 0; fg = fg < g_last ? fg + 1 : g_last; }
         };
