@@ -164,9 +164,10 @@ int tb200_matmul_plain(const void* a, const void* b, void* out, int64_t m, int64
  *   out     fp16  [m, ldo]; this call writes columns [col_offset, col_offset + n) — an N-partitioned
  *           rank passes its slice of wp/scales and the offset of its slice in the full output
  *   out[i, col_offset + j] = fp16( sum_k float(a[i,k]) * float(fp16((q[j,k]-zp) * scales[j,k/group])) )
- *   workspace  fp32 scratch for the split-K variant chosen for 17 <= m <= 64; size from
- *              tb200_gemm_w4a16_workspace_bytes(), which holds for every valid group; may be NULL when
- *              that returns 0 (always the case for m <= 16 and m > 64)
+ *   workspace  fp32 scratch for the split-K variant, which is chosen for 17 <= m <= 64 when the weight has few
+ *              128-row tiles (n / 128 under half the SM count); size from tb200_gemm_w4a16_workspace_bytes(),
+ *              which holds for every valid group; may be NULL when that returns 0 (always the case for
+ *              m <= 16 and m > 64)
  * n a multiple of 128, k a multiple of 128.
  */
 size_t tb200_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k);
@@ -192,8 +193,8 @@ int tb200_gemm_w4a16_gather(const void* a, const void* wp_local, const void* sca
 /*
  * W4A16 GEMM for callers that cannot allocate device memory.  No counterpart in the reference.
  *
- * tb200_gemm_w4a16 asks its caller for a split-K workspace when m is small (17..64 rows; fewer rows take a
- * streaming kernel that needs none).  Some callers have
+ * tb200_gemm_w4a16 asks its caller for a split-K workspace when m is small (17..64 rows) and the weight is
+ * narrow (fewer rows take a streaming kernel that needs none).  Some callers have
  * no way to provide one: a plugin running inside a host process that has handed all device memory to its
  * own pool, or code invoked where cudaMalloc is not permitted.  This variant computes the same result
  * with the partial sums kept in a fixed array of TB200_W4A16_STATIC_SCRATCH_BYTES that is part of the

@@ -223,7 +223,7 @@ def test_w4a16_short_k_fewer_blocks_than_issuers(cuda_device, M, N, K):
     np.testing.assert_allclose(got, want, **FP16_TOL)
 
 
-@pytest.mark.parametrize("M", [1, 16, 128])
+@pytest.mark.parametrize("M", [1, 16, 17, 40, 64, 128])
 def test_w4a16_config_shapes_small_m(cuda_device, M):
     got, want = w4_case(M, 14336, 4096, seed=50 + M, device=cuda_device)
     np.testing.assert_allclose(got, want, **FP16_TOL)
@@ -292,10 +292,10 @@ def test_w4a16_column_offset_writes_only_its_slice(cuda_device, M):
 
 def test_w4a16_workspace_too_small_is_an_error(cuda_device):
     ext = native.load()
-    a, wp, sc, group, zp = tensors.generate_gemm_w4a16_inputs(24, 4096, 14336, device=cuda_device, seed=9)
-    if ext.gemm_w4a16_workspace_bytes(24, 14336, 4096) == 0:
-        pytest.skip("no split-K for this shape")
-    out = torch.empty(24, 14336, dtype=torch.float16, device=cuda_device)
+    a, wp, sc, group, zp = tensors.generate_gemm_w4a16_inputs(24, 4096, 4096, device=cuda_device, seed=9)
+    assert ext.gemm_w4a16_workspace_bytes(24, 4096, 4096) > 0        # narrow weight: the split-K path
+    assert ext.gemm_w4a16_workspace_bytes(24, 14336, 4096) == 0      # wide weight: one wave of 128-row tiles, no scratch
+    out = torch.empty(24, 4096, dtype=torch.float16, device=cuda_device)
     with pytest.raises(ValueError):
         ext.gemm_w4a16(a, wp, sc, out, group, zp, 0, None)
 

@@ -44,10 +44,10 @@ def test_static_scratch_matches_workspace_entry_point_twice(cuda_device):
     lib = native.capi()
     assert lib.tb200_gemm_w4a16_static_scratch_bytes() == 16 << 20
     native.clear_device_status()
-    # small m above the streaming kernel's range on the benchmark's weight shape: the tensor-memory
+    # small m above the streaming kernel's range on a narrow weight (32 tiles of 128 rows): the tensor-memory
     # GEMM splits K there, so the built-in array is really used
     for seed, m in ((101, 24), (202, 17)):
-        need, got, ref = run_pair(lib, cuda_device, m, 14336, 4096, seed)
+        need, got, ref = run_pair(lib, cuda_device, m, 4096, 4096, seed)
         assert 0 < need <= 16 << 20
         assert not torch.isnan(got).any()
         assert torch.equal(got, ref)
@@ -61,7 +61,7 @@ def test_static_entry_point_without_scratch_and_over_the_limit(cuda_device):
     assert torch.equal(got, ref)
     # a shape whose partial sums do not fit is refused with a message, not run
     m, k = 64, 4096
-    n = next((c for c in (14336, 28672, 57344, 8192) if lib.tb200_gemm_w4a16_workspace_bytes(m, c, k) > 16 << 20), None)
+    n = next((c for c in (9216, 8192, 7168, 6144) if lib.tb200_gemm_w4a16_workspace_bytes(m, c, k) > 16 << 20), None)
     if n is None:
         pytest.skip("no probe shape exceeds the built-in array on this device")
     t = torch.zeros(16, dtype=torch.uint8, device=cuda_device)

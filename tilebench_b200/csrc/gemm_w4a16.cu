@@ -24,8 +24,8 @@
 //                     activation stage and the operand stage (same barrier).  Small-N MMAs finish in
 //                     fewer cycles than one thread needs to issue them, so decode-sized tiles use
 //                     several issuers; private accumulators keep the summation order fixed.
-//   warps 6..7        idle (keep the following warp quads aligned with the TMEM lane quarters)
-//   warps 8..         convert warps (kDQ groups of 4 taking K blocks in turn): thread = weight row;
+//   (idle warps)      up to the next multiple of four (the following warp quads align with the TMEM lane quarters)
+//   warps 4.. / 8..   convert warps (kDQ groups of 4 taking K blocks in turn): thread = weight row;
 //                     2 x LDS.128 of packed nibbles -> 64 fp16 -> tcgen05.st into an operand stage
 //   next 4 warps      epilogue: tcgen05.ld the finished accumulators (summed in issuer order), cast;
 //                     for MT >= 128 transpose
@@ -52,7 +52,7 @@ template <int MT> struct W4Cfg {
     // (barrier hops, LDS, ~140 dependent ALU instructions, tcgen05.st), so two groups deliver a block every
     // ~0.5 us whatever the tile size.  That is below the MMA time of the 256-row tile, but it is what bounds
     // the 128-row tile (m of 65..128, one wave of CTAs): a third group there is worth 10-15 %.
-    static constexpr int kDQ = MT == 128 ? 3 : 2;
+    static constexpr int kDQ = MT == 128 ? 4 : 2;
     static constexpr int kActStageBytes = MT * kBK * 2;          // one [MT x 64] fp16 activation tile
     static constexpr int kNI = MT <= 32 ? 4 : (MT <= 128 ? 2 : 1);   // MMA issuer threads, one accumulator each
     static constexpr int kNAcc = MT >= 128 ? 1 : 2;              // accumulator sets (double-buffered when they fit)
@@ -69,7 +69,10 @@ template <int MT> struct W4Cfg {
     static constexpr int kTmemCols = kTmemNeed <= 32 ? 32 : kTmemNeed <= 64 ? 64 : kTmemNeed <= 128 ? 128
                                      : kTmemNeed <= 256 ? 256 : 512;
     static constexpr int kMmaWarp0 = 2;
-    static constexpr int kCvtWarp0 = 8;
+    // convert warps start at a multiple of four (a warp reaches the TMEM lane quarter warp % 4): right behind the
+    // issuers when there are at most two of them, which is what lets the 128-row tile run four convert groups
+    // in the 768 threads that held three
+    static constexpr int kCvtWarp0 = kNI <= 2 ? 4 : 8;
     static constexpr int kEpiWarp0 = kCvtWarp0 + 4 * kDQ;
     static constexpr int kWarps = kEpiWarp0 + 4;
     static constexpr int kThreads = 32 * kWarps;
@@ -543,7 +546,15 @@ TB200_DEFINE_STATUS_HOOKS(gemm_w4a16)
 
 namespace {
 
-int pick_mt(int64_t m) { return m <= 16 ? 16 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)); }
+// Activation-row tile (= MMA N).  17..64 rows: the 64-row tile with split-K only pays when there are few weight
+// tiles to spread (n / 128 under half the SM count); otherwise the 128-row tile in one wave is faster although
+// most of its MMA is padding, because the kernel is paced by the weight conversion, not by the MMA (measured at
+// n = 14336, k = 4096: 34-44 us split against 27.5 us unsplit).
+int pick_mt(int64_t m, int64_t n) {
+    if (m <= 16) return 16;
+    if (m <= 64) return (n / kBNW) * 2 > num_sms() ? 128 : 64;
+    return m <= 128 ? 128 : 256;
+}
 
 // Shapes of at most kGemvMaxM activation rows go to the streaming mma.sync kernel (gemv_w4a16.cu).
 constexpr int64_t kGemvMaxM = 16;
@@ -553,7 +564,7 @@ bool use_gemv(int64_t m, int64_t group) { return m <= kGemvMaxM && group % 128 =
 // pick the split that fills whole waves of SMs best.  Every split keeps at least 4 K blocks, which
 // also guarantees each MMA issuer thread its own block.
 int pick_splitk(int64_t m, int64_t n, int64_t k) {
-    const int mt = pick_mt(m);
+    const int mt = pick_mt(m, n);
     // m <= 16 never splits K: with group a multiple of 128 those shapes take the streaming kernel, and with
     // any other group the tensor-memory kernel runs unsplit, so that the workspace query (which does not
     // know the group) can promise "no workspace" for every decode-sized call
@@ -675,7 +686,7 @@ int gemm_w4a16_impl(const void* a, const void* wp, const void* scales, void* out
         if (!aligned16(workspace)) return fail(TB200_ERR_ALIGN, "gemm_w4a16: workspace must be 16-byte aligned");
         ws = static_cast<float*>(workspace);
     }
-    switch (pick_mt(m)) {
+    switch (pick_mt(m, n)) {
         case 16:  return launch_w4<16>(tb200_k_gemm_w4a16_m16, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, peers, st);
         case 64:  return launch_w4<64>(tb200_k_gemm_w4a16_m64, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, peers, st);
         case 128: return launch_w4<128>(tb200_k_gemm_w4a16_m128, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, peers, st);
