@@ -50,9 +50,10 @@ constexpr int kGroupN = 16;    // tile-order grouping for L2 reuse
 template <int MT> struct W4Cfg {
     // Convert warp groups; group g takes the K blocks with it % kDQ == g.  One group needs about 1 us per K block
     // (barrier hops, LDS, ~140 dependent ALU instructions, tcgen05.st), so two groups deliver a block every
-    // ~0.5 us whatever the tile size.  That is below the MMA time of the 256-row tile, but it is what bounds
-    // the 128-row tile (m of 65..128, one wave of CTAs): a third group there is worth 10-15 %.
-    static constexpr int kDQ = MT == 128 ? 4 : 2;
+    // ~0.5 us whatever the tile size.  The 128-row tile (one wave of CTAs) is bound by exactly that: three groups
+    // were worth 12 %, a fourth another 6 % once it fitted the same 768 threads.  The 256-row tile gains 2-4 %
+    // from a third group and loses it again with a fourth (80 registers per thread at 768 threads).
+    static constexpr int kDQ = MT == 128 ? 4 : (MT == 256 ? 3 : 2);
     static constexpr int kActStageBytes = MT * kBK * 2;          // one [MT x 64] fp16 activation tile
     static constexpr int kNI = MT <= 32 ? 4 : (MT <= 128 ? 2 : 1);   // MMA issuer threads, one accumulator each
     static constexpr int kNAcc = MT >= 128 ? 1 : 2;              // accumulator sets (double-buffered when they fit)
