@@ -261,6 +261,17 @@ def test_int4_group_quantiser_bit_exact_and_round_trip(cuda_device, N, K):
     assert torch.all((x - back).abs() <= 0.51 * step)       # half a step + fp16 rounding of (q - zp) * s
 
 
+def test_int4_group_quantiser_out_of_range_group(cuda_device):
+    # amax / 7 beyond the fp16 range: infinite scale, every code of that group is the zero point (same as the formula)
+    from tilebench_b200.benchmarks.operators.quantize_int4_group import impl_cuda
+    x = torch.full((2, 256), 0.25)
+    x[0, 3] = 1.0e6
+    wp, s = impl_cuda.run(x.to(cuda_device), 128, 8)
+    owp, osc = ref_ops.quantize_int4_group(x.numpy())
+    assert np.array_equal(wp.cpu().numpy(), owp) and np.array_equal(bits16(s), osc.view(np.uint16))
+    assert torch.isinf(s[0, 0]) and np.all(ref_ops.unpack_int4(owp)[0, :128] == 8)
+
+
 def test_int4_group_quantiser_rejects_other_groups(cuda_device):
     ext = native.load()
     x = torch.zeros(4, 256, device=cuda_device)
