@@ -484,14 +484,33 @@ def run_ours(args):
 
     for _ in range(args.warmup):
         step()
+    torch.cuda.synchronize()
+    # the K timed steps are K kernel launches replayed as one CUDA graph (host launch cost stays out of a device
+    # measurement); if capture is not possible they are launched one by one
+    run_steps, launch_mode = (lambda: [step() for _ in range(args.steps)]), "eager launches"
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(args.steps):
+                step()
+        graph.replay()                                   # one untimed replay: graph upload
+        torch.cuda.synchronize()
+        run_steps, launch_mode = graph.replay, f"one CUDA graph of {args.steps} kernel launches"
+    except Exception:
+        torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     sampler.busy(True)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(args.steps):
-        step()
+    run_steps()
     end.record()
     end.synchronize()
     torch.cuda.synchronize()
@@ -566,6 +585,7 @@ def run_ours(args):
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": workload_config(world),
+            "timed_region": launch_mode,
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": per_gpu / peaks["hbm_gbs"], "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
                          "peak_source": f"of {peaks['source']}", "kernel": "tb200_k_dequant_int8_rowwise_bf16_wide",

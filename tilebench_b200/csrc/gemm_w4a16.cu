@@ -342,8 +342,6 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 const uint8_t* wt = w_ring + sw * kWBytes;
                 const uint4 p0 = *reinterpret_cast<const uint4*>(wt + off0);
                 const uint4 p1 = *reinterpret_cast<const uint4*>(wt + off1);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_wempty[sw]);     // packed bytes are in registers
                 const __half2 s2h = __half2half2(s0);
                 uint32_t frag[32];
                 const uint32_t pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
@@ -355,6 +353,12 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                     frag[4 * i + 2] = dq_pair(lo, hi, 0x0602, bias, s2h);
                     frag[4 * i + 3] = dq_pair(lo, hi, 0x0703, bias, s2h);
                 }
+                // The packed stage is released only now, after the unpack has CONSUMED p0 / p1.  Releasing it right
+                // after the two loads were issued let the TMA refill overtake loads still in flight: a few weight
+                // rows of one K block then came from the wrong block (seen as run-to-run differences in single
+                // output columns, about once in twenty calls of a 7168-tile problem with three convert groups).
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_wempty[sw]);
                 if (it >= static_cast<uint32_t>(AST)) {      // the MMAs that last read this operand stage
                     const uint32_t j = it - AST;
                     if (!mbar_wait(&bar_done[j % SA], (j / SA) & 1, ST_WAIT_OPERAND, -kb - 1)) { ok = false; break; }
