@@ -501,3 +501,47 @@ def test_plain_bf16_matches_fp32_reference(cuda_device, M, N, K):
     eye = torch.eye(512, dtype=torch.bfloat16, device=cuda_device)
     bb = torch.randint(-8, 9, (512, 256), dtype=torch.int32).to(torch.bfloat16).to(cuda_device)
     assert torch.equal(plain_run(eye, bb), bb)
+
+
+# ---------------------------------------------------------------- run-to-run identity of every tensor-core kernel
+
+@pytest.mark.parametrize("which", ["fp8_4096", "fp8_ragged_pair", "int8_k20480", "plain_f16", "plain_tf32", "plain_e4m3"])
+def test_gemm_kernels_repeated_calls_are_bit_identical(cuda_device, monkeypatch, which):
+    """Every GEMM here sums in a fixed order, so identical calls must give identical bits; a difference is a race
+    (a stage or accumulator handed over too early).  Many repeats with the caches disturbed in between."""
+    ext = native.load()
+    g = torch.Generator(device=cuda_device).manual_seed(5)
+    if which.startswith("fp8"):
+        if which == "fp8_ragged_pair":
+            monkeypatch.setenv("TB200_FP8_VARIANT", "pair")
+            M, N, K, reps = 3000, 4096, 2048, 100
+        else:
+            M, N, K, reps = 4096, 4096, 4096, 100
+        aq, sa = tensors.quantize_fp8_blockwise(torch.randn(M, K, device=cuda_device, generator=g), 1, 128)
+        bq, sb = tensors.quantize_fp8_blockwise(torch.randn(N, K, device=cuda_device, generator=g), 128, 128)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=cuda_device)
+        call = lambda: ext.gemm_fp8_blockscaled(aq, sa, bq, sb, out)
+    elif which == "int8_k20480":
+        M, N, K, reps = 2048, 2048, 20480, 100
+        a = torch.randint(-64, 65, (M, K), dtype=torch.int8, device=cuda_device, generator=g)
+        b = torch.randint(0, 256, (K // 4, N), dtype=torch.uint8, device=cuda_device, generator=g)
+        out = torch.empty(M, N, dtype=torch.int32, device=cuda_device)
+        call = lambda: ext.matmul_int8_packed2(a, b, out)
+    else:
+        dt = {"plain_f16": torch.float16, "plain_tf32": torch.float32, "plain_e4m3": torch.float8_e4m3fn}[which]
+        M, N, K, reps = 4096, 4096, 4096, 60
+        a = (torch.randn(M, K, device=cuda_device, generator=g) * K ** -0.5).to(dt)
+        b = (torch.randn(K, N, device=cuda_device, generator=g) * K ** -0.5).to(dt)
+        out = torch.empty(M, N, dtype=dt, device=cuda_device)
+        call = lambda: ext.matmul_plain(a, b, out)
+    native.clear_device_status()
+    call()
+    first = out.clone().view(torch.uint8)
+    scratch = torch.empty(32 << 20, dtype=torch.float32, device=cuda_device)
+    for r in range(reps):
+        if r % 3 == 0:
+            scratch.fill_(float(r))
+        out.view(torch.uint8).fill_(0xAA)
+        call()
+        assert torch.equal(out.view(torch.uint8), first), f"{which}: call {r} differs from the first"
+    status_clean()
