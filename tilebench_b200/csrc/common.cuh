@@ -127,6 +127,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe of a phase (mbarrier.test_wait never suspends the thread): used to look at the NEXT
+// stage's barriers between two instructions of the current one, so that the probe's latency is hidden and
+// the blocking wait below is skipped when the answer was already "complete".
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: polls until the phase completes or kWaitCycles SM clock cycles have passed (about
 // two seconds — far longer than any legitimate wait here, a whole kernel runs in milliseconds).
 // The bound uses the SM-local cycle counter: reading it costs a few cycles, unlike the global

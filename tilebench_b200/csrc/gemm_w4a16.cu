@@ -261,38 +261,62 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         }
     } else if (warp >= Cfg::kMmaWarp0 && warp < Cfg::kMmaWarp0 + NI) {
         // ---------------- MMA issuers ----------------
+        // The issuing thread is the pacemaker of the large tiles (four MMAs of 128 tensor-pipe cycles each per
+        // K block leave it about 500 cycles for everything), so its loop carries no division, no branch
+        // that is not needed and no wait that can be avoided: the K blocks of issuer `me` are the running
+        // counts me, me + NI, ... across work items; ring slots and phases advance by addition; the shared-
+        // memory descriptor is a base plus a slot offset; and the barriers of the NEXT block are probed
+        // (non-blocking) between the first and second MMA of the current one, so the blocking wait
+        // is skipped whenever the convert warps and the activation copies are ahead.
         if (lane == 0) {
-            const int me = warp - Cfg::kMmaWarp0;                    // K blocks with it % NI == me are mine
+            const uint32_t me = warp - Cfg::kMmaWarp0;
             constexpr uint32_t idesc_full = umma_idesc(0, 0, kBNW, MT);   // f16 x f16 -> f32, M = 128, N = MT
             constexpr uint32_t idesc_half = umma_idesc(0, 0, kBNW, 128);  // N = 128 for a half unit of the 256-row tile
-            uint32_t it = 0, item_cnt = 0;
+            constexpr uint32_t kStageDesc = Cfg::kActStageBytes >> 4;     // one activation stage in descriptor units
+            static_assert(NI <= SA && NI <= AST, "an issuer advances by NI slots per K block");
+            const uint64_t b_desc0 = umma_desc_sw128(smem_u32(act_ring));
+            const uint32_t a_tmem0 = tmem_base + Cfg::kACol0;
+            uint32_t my_it = me;                 // running count of my next K block
+            uint32_t sa = me, pa = 0;            // its activation slot and phase
+            uint32_t so = me, po = 0;            // its operand slot and phase
+            uint32_t it0 = 0, item_cnt = 0;
+            bool ready = false;                  // my next block's barriers were seen complete already
             bool ok = true;
             for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++item_cnt) {
                 const Item im = make_item(w, sched);
+                const uint32_t it_end = it0 + static_cast<uint32_t>(im.kb1 - im.kb0);
                 const int acc = acc_of(item_cnt);
                 const uint32_t idesc = (MT == 256 && im.half >= 0) ? idesc_half : idesc_full;
                 const uint32_t d_tmem = tmem_base + (acc * NI + me) * MT;
                 // the accumulator set must have been drained before this item's first MMA overwrites it
                 if (!mbar_wait(&bar_dempty[acc], (acc_use(item_cnt) & 1) ^ 1, ST_WAIT_TMEM_EMPTY, w)) { ok = false; break; }
-                bool first = true;
-                for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
-                    if (NI > 1 && static_cast<int>(it % NI) != me) continue;
-                    const int s = it % SA;
-                    const int os = it % AST;
-                    if (!mbar_wait(&bar_ofull[os], (it / AST) & 1, ST_WAIT_OPERAND, kb)) { ok = false; break; }
-                    if (!mbar_wait(&bar_afull[s], (it / SA) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t a_tmem = tmem_base + Cfg::kACol0 + os * 32;
-                    const uint64_t b_desc = umma_desc_sw128(smem_u32(act_ring + s * Cfg::kActStageBytes));
-#pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k) {
-                        // 16 fp16 of K = 8 TMEM columns of the operand, 32 bytes of the swizzled smem row
-                        umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
+                uint32_t accumulate = 0u;
+                while (my_it < it_end) {
+                    if (!ready) {
+                        const int kb = im.kb0 + static_cast<int>(my_it - it0);
+                        if (!mbar_wait(&bar_ofull[so], po, ST_WAIT_OPERAND, kb)) { ok = false; break; }
+                        if (!mbar_wait(&bar_afull[sa], pa, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
                     }
-                    first = false;
-                    tc_commit(&bar_done[s]);
+                    tc_fence_after();
+                    const uint32_t a_tmem = a_tmem0 + so * 32;
+                    const uint64_t b_desc = b_desc0 + sa * kStageDesc;
+                    uint64_t* const done = &bar_done[sa];
+                    sa += NI; if (sa >= static_cast<uint32_t>(SA)) { sa -= SA; pa ^= 1; }
+                    so += NI; if (so >= static_cast<uint32_t>(AST)) { so -= AST; po ^= 1; }
+                    // 16 fp16 of K = 8 TMEM columns of the operand, 32 bytes of the swizzled smem row
+                    umma_f16_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+                    const bool next_o = mbar_test_wait(&bar_ofull[so], po);
+                    const bool next_a = mbar_test_wait(&bar_afull[sa], pa);
+#pragma unroll
+                    for (int k = 1; k < kBK / 16; ++k) umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, 1u);
+                    // "MMAs of this K block complete": frees the activation slot and the operand slot
+                    tc_commit(done);
+                    accumulate = 1u;
+                    ready = next_o && next_a;
+                    my_it += NI;
                 }
                 if (ok) tc_commit(&bar_dfull[acc]);   // one arrival per issuer; every issuer had >= 1 K block
+                it0 = it_end;
             }
         }
     } else if (warp >= Cfg::kCvtWarp0 && warp < Cfg::kEpiWarp0) {
@@ -306,43 +330,58 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         const uint32_t swz = ((row >> 2) & 1) << 4;
         const uint32_t off0 = row * 32 + (0u ^ swz), off1 = row * 32 + (16u ^ swz);
         const int g_last = groups_per_row - 1;
-        auto scale_at = [&](const __half* srow, int g) { return __ldg(srow + min(g, g_last)); };
+        // scale of this thread's weight row for K block kb (clamped into the row, so look-ahead never leaves it)
+        auto scale_kb = [&](const __half* srow, int kb) { return __ldg(srow + min(kb / kb_per_group, g_last)); };
         auto scale_row = [&](const Item& im) {
             return scales + static_cast<int64_t>(im.n_blk * kBNW + row) * groups_per_row;
         };
-        // Scales are fetched three groups ahead of their use (s0 = current group), and the first
-        // three of the next work item while the current one runs, so no load sits on the K loop.
+        // Scales travel in a three-deep queue indexed by this group's VISITS (K blocks kb, kb + DQ, kb + 2 DQ):
+        // a value is loaded two visits before it is used and only moved between registers a whole visit
+        // after its load was issued, so no instruction waits on a load in flight whatever the ratio of
+        // DQ to the K blocks per scale group.  The first three of the next work item are fetched while
+        // the current one runs.
+        // This group's K blocks are the running counts grp, grp + DQ, ... across work items; ring slots and
+        // phases advance by addition (no division and no skipped iterations in the loop).
+        static_assert(DQ <= SW && DQ <= AST && DQ <= SA, "a convert group advances by DQ slots per visit");
+        uint32_t my_it = grp;                            // running count of my next K block
+        uint32_t sw = grp, phw = 0;                      // its packed-weight slot and phase
+        uint32_t os = grp;                               // its operand slot
+        // "MMAs complete" slot and phase of the block that used operand slot os before (running count
+        // my_it - AST), meaningful from the first visit with my_it >= AST on
+        uint32_t first_reuse = grp;
+        while (first_reuse < static_cast<uint32_t>(AST)) first_reuse += DQ;
+        uint32_t sd = (first_reuse - AST) % SA, pd = ((first_reuse - AST) / SA) & 1;
         __half s0, s1, s2, n0 = __half(), n1 = __half(), n2 = __half();
         if (static_cast<int>(blockIdx.x) < items) {
             const Item im = make_item(blockIdx.x, sched);
             const __half* srow = scale_row(im);
-            const int g = im.kb0 / kb_per_group;
-            n0 = scale_at(srow, g); n1 = scale_at(srow, g + 1); n2 = scale_at(srow, g + 2);
+            const int kbf = im.kb0 + grp;
+            n0 = scale_kb(srow, kbf); n1 = scale_kb(srow, kbf + DQ); n2 = scale_kb(srow, kbf + 2 * DQ);
         }
-        uint32_t it = 0;
+        uint32_t it0 = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
             const Item im = make_item(w, sched);
+            const uint32_t it_end = it0 + static_cast<uint32_t>(im.kb1 - im.kb0);
             const __half* srow = scale_row(im);
-            int gcur = im.kb0 / kb_per_group;
             s0 = n0; s1 = n1; s2 = n2;
             if (w + static_cast<int>(gridDim.x) < items) {
                 const Item nx = make_item(w + gridDim.x, sched);
                 const __half* nrow = scale_row(nx);
-                const int g = nx.kb0 / kb_per_group;
-                n0 = scale_at(nrow, g); n1 = scale_at(nrow, g + 1); n2 = scale_at(nrow, g + 2);
+                const uint32_t rem = it_end > my_it ? it_end - my_it : 0u;
+                const uint32_t my_next = my_it + (rem + DQ - 1) / DQ * DQ;      // my first K block past this item
+                const int kbf = nx.kb0 + static_cast<int>(my_next - it_end);
+                n0 = scale_kb(nrow, kbf); n1 = scale_kb(nrow, kbf + DQ); n2 = scale_kb(nrow, kbf + 2 * DQ);
             }
-            for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
-                if (static_cast<int>(it % DQ) != grp) continue;
-                const int sw = it % SW;
-                const int os = it % AST;
-                const int g = kb / kb_per_group;
-                while (gcur < g) { s0 = s1; s1 = s2; s2 = scale_at(srow, gcur + 3); ++gcur; }
-                if (!mbar_wait(&bar_wfull[sw], (it / SW) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
+            for (; my_it < it_end; my_it += DQ) {
+                const int kb = im.kb0 + static_cast<int>(my_it - it0);
+                const __half s_cur = s0;
+                s0 = s1; s1 = s2; s2 = scale_kb(srow, kb + 3 * DQ);
+                if (!mbar_wait(&bar_wfull[sw], phw, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
                 const uint8_t* wt = w_ring + sw * kWBytes;
                 const uint4 p0 = *reinterpret_cast<const uint4*>(wt + off0);
                 const uint4 p1 = *reinterpret_cast<const uint4*>(wt + off1);
-                const __half2 s2h = __half2half2(s0);
+                const __half2 s2h = __half2half2(s_cur);
                 uint32_t frag[32];
                 const uint32_t pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
 #pragma unroll
@@ -359,9 +398,9 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 // output columns, about once in twenty calls of a 7168-tile problem with three convert groups).
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_wempty[sw]);
-                if (it >= static_cast<uint32_t>(AST)) {      // the MMAs that last read this operand stage
-                    const uint32_t j = it - AST;
-                    if (!mbar_wait(&bar_done[j % SA], (j / SA) & 1, ST_WAIT_OPERAND, -kb - 1)) { ok = false; break; }
+                if (my_it >= static_cast<uint32_t>(AST)) {   // the MMAs that last read this operand stage
+                    if (!mbar_wait(&bar_done[sd], pd, ST_WAIT_OPERAND, -kb - 1)) { ok = false; break; }
+                    sd += DQ; if (sd >= static_cast<uint32_t>(SA)) { sd -= SA; pd ^= 1; }
                 }
                 tc_fence_after();
                 tmem_st32(t_lane + os * 32, frag);
@@ -369,7 +408,10 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_ofull[os]);
+                sw += DQ; if (sw >= static_cast<uint32_t>(SW)) { sw -= SW; phw ^= 1; }
+                os += DQ; if (os >= static_cast<uint32_t>(AST)) os -= AST;
             }
+            it0 = it_end;
         }
     } else if (warp >= Cfg::kEpiWarp0) {
         // ---------------- epilogue warps ----------------
