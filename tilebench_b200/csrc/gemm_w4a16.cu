@@ -163,6 +163,10 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
     constexpr int DQ = Cfg::kDQ;
     constexpr int NACC = Cfg::kNAcc;
     constexpr int NI = Cfg::kNI;
+    // With equally deep activation and operand rings a K block uses the same slot in both, so ONE barrier per
+    // slot collects the activation copy (expect-tx arrival of the producer) and the four convert warps: the
+    // issuer waits on, and probes, a single barrier per K block.
+    constexpr bool kMerged = SA == AST;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* act_ring = smem;
@@ -189,7 +193,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
     auto acc_use = [](uint32_t item_cnt) { return NACC == 1 ? item_cnt : (item_cnt >> 1); };
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < SA; ++s) { mbar_init(&bar_afull[s], 1); mbar_init(&bar_done[s], 1); }
+        for (int s = 0; s < SA; ++s) { mbar_init(&bar_afull[s], kMerged ? 5 : 1); mbar_init(&bar_done[s], 1); }
         for (int s = 0; s < SW; ++s) { mbar_init(&bar_wfull[s], 1); mbar_init(&bar_wempty[s], 4); }
         for (int s = 0; s < AST; ++s) mbar_init(&bar_ofull[s], 4);
         for (int b = 0; b < 2; ++b) { mbar_init(&bar_dfull[b], NI); mbar_init(&bar_dempty[b], 4); }
@@ -231,7 +235,9 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 for (int s = 0; s < SA; ++s) {
                     if (it > static_cast<uint32_t>(s)) {
                         uint32_t last = it - 1 - ((it - 1 - s) % SA);
-                        (void)mbar_wait(&bar_afull[s], (last / SA) & 1, ST_WAIT_SMEM_FULL, -1);
+                        // (short limit: with the merged barrier the phase also needs the convert warps, which
+                        // may have left already)
+                        (void)mbar_wait_limit(&bar_afull[s], (last / SA) & 1, ST_WAIT_SMEM_FULL, -1, 1ll << 22);
                     }
                 }
             }
@@ -268,7 +274,12 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         // memory descriptor is a base plus a slot offset; and the barriers of the NEXT block are probed
         // (non-blocking) between the first and second MMA of the current one, so the blocking wait
         // is skipped whenever the convert warps and the activation copies are ahead.
-        if (lane == 0) {
+        // The WHOLE warp walks the loop (waits, probes, slot arithmetic are warp-uniform); only the MMAs and the
+        // commits are issued by lane 0.  Running the loop inside an `if (lane == 0)` region instead made every
+        // branch of the lone thread cost 100-250 cycles (measured with the cycle counter: 257 cycles for the loop's
+        // back edge, 95 for a not-taken `if`), which alone held the 256-row tile to about half the tensor rate.
+        {
+            const bool leader = lane == 0;
             const uint32_t me = warp - Cfg::kMmaWarp0;
             constexpr uint32_t idesc_full = umma_idesc(0, 0, kBNW, MT);   // f16 x f16 -> f32, M = 128, N = MT
             constexpr uint32_t idesc_half = umma_idesc(0, 0, kBNW, 128);  // N = 128 for a half unit of the 256-row tile
@@ -294,7 +305,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 while (my_it < it_end) {
                     if (!ready) {
                         const int kb = im.kb0 + static_cast<int>(my_it - it0);
-                        if (!mbar_wait(&bar_ofull[so], po, ST_WAIT_OPERAND, kb)) { ok = false; break; }
+                        if (!kMerged && !mbar_wait(&bar_ofull[so], po, ST_WAIT_OPERAND, kb)) { ok = false; break; }
                         if (!mbar_wait(&bar_afull[sa], pa, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
                     }
                     tc_fence_after();
@@ -304,18 +315,20 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                     sa += NI; if (sa >= static_cast<uint32_t>(SA)) { sa -= SA; pa ^= 1; }
                     so += NI; if (so >= static_cast<uint32_t>(AST)) { so -= AST; po ^= 1; }
                     // 16 fp16 of K = 8 TMEM columns of the operand, 32 bytes of the swizzled smem row
-                    umma_f16_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
-                    const bool next_o = mbar_test_wait(&bar_ofull[so], po);
+                    if (leader) umma_f16_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+                    const bool next_o = kMerged ? true : mbar_test_wait(&bar_ofull[so], po);
                     const bool next_a = mbar_test_wait(&bar_afull[sa], pa);
+                    if (leader) {
 #pragma unroll
-                    for (int k = 1; k < kBK / 16; ++k) umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, 1u);
-                    // "MMAs of this K block complete": frees the activation slot and the operand slot
-                    tc_commit(done);
+                        for (int k = 1; k < kBK / 16; ++k) umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, 1u);
+                        // "MMAs of this K block complete": frees the activation slot and the operand slot
+                        tc_commit(done);
+                    }
                     accumulate = 1u;
                     ready = next_o && next_a;
                     my_it += NI;
                 }
-                if (ok) tc_commit(&bar_dfull[acc]);   // one arrival per issuer; every issuer had >= 1 K block
+                if (ok && leader) tc_commit(&bar_dfull[acc]);   // one arrival per issuer; every issuer had >= 1 K block
                 it0 = it_end;
             }
         }
@@ -407,7 +420,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_ofull[os]);
+                if (lane == 0) mbar_arrive(kMerged ? &bar_afull[os] : &bar_ofull[os]);
                 sw += DQ; if (sw >= static_cast<uint32_t>(SW)) { sw -= SW; phw ^= 1; }
                 os += DQ; if (os >= static_cast<uint32_t>(AST)) os -= AST;
             }
