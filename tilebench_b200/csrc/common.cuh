@@ -340,6 +340,16 @@ __device__ __forceinline__ void umma_f8_ss_pair(uint32_t d_tmem, uint64_t a_desc
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// D[tmem of both CTAs] (+)= A[tmem, 128 lanes per CTA] * B[smem, half of N per CTA]; issued by the leader only.
+__device__ __forceinline__ void umma_f16_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // All MMAs issued so far by this thread arrive, once complete, on `bar` in every CTA of `cta_mask`.
 __device__ __forceinline__ void tc_commit_pair(uint64_t* bar, uint16_t cta_mask) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"

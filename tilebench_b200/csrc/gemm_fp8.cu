@@ -158,7 +158,7 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
     uint64_t* bar_tempty = bar_empty + S;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);   // uniform for the compiler
     const int lane = threadIdx.x & 31;
     const int KB = K / kBK;
     const int tiles_m = (M + kBM - 1) / kBM;
@@ -235,34 +235,47 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
         // CTA's running count, warp 2 the odd ones.  Every K block starts a fresh accumulator, so the
         // two instruction streams are independent; each thread's waits and issue cost (several
         // hundred cycles per K block) overlap the other's.
-        if (lane == 0) {
+        // The whole warp walks the loop and lane 0 issues: the branches of a lone thread inside an
+        // `if (lane == 0)` region cost 100-250 cycles each (measured), and this thread's reaction time — buffer
+        // released -> first MMA issued — is part of the dependency loop that paces the kernel.
+        {
             constexpr uint32_t idesc_wide = umma_idesc(0, 0, kBM, BN);  // e4m3 x e4m3 -> f32
             constexpr uint32_t idesc_half = umma_idesc(0, 0, kBM, 128);
+            constexpr uint32_t kStageDesc = Cfg::kStageBytes >> 4;
+            static_assert(S >= 2 && S % 2 == 0, "two issuers advance by two stages per block");
+            const bool leader = lane == 0;
             const uint32_t me = warp - 1;
-            uint32_t it = 0;
+            const uint64_t a_desc0 = umma_desc_sw128(smem_u32(smem));
+            const uint64_t b_desc0 = umma_desc_sw128(smem_u32(smem) + Cfg::kABytes);
+            const uint32_t d_tmem = tmem_base + me * BN;               // buffer = running count & 1 = me
+            uint32_t my_it = me, s = me, ph = 0, pt = 1;               // pt: phase to wait for on "buffer free"
+            uint32_t it0 = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
                 const uint32_t idesc = u < wide_units ? idesc_wide : idesc_half;
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    if ((it & 1) != me) continue;
-                    const int s = it % S;
-                    const int buf = it & 1;
-                    if (!mbar_wait(&bar_tempty[buf], ((it >> 1) & 1) ^ 1, ST_WAIT_TMEM_EMPTY, kb)) { ok = false; break; }
-                    if (!mbar_wait(&bar_full[s], (it / S) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
+                const uint32_t it_end = it0 + static_cast<uint32_t>(KB);
+                while (my_it < it_end) {
+                    const int kb = static_cast<int>(my_it - it0);
+                    if (!mbar_wait(&bar_tempty[me], pt, ST_WAIT_TMEM_EMPTY, kb)) { ok = false; break; }
+                    if (!mbar_wait(&bar_full[s], ph, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes);
-                    const uint64_t a_desc = umma_desc_sw128(a_addr);
-                    const uint64_t b_desc = umma_desc_sw128(a_addr + Cfg::kABytes);
-                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    if (leader) {
+                        const uint64_t a_desc = a_desc0 + s * kStageDesc;
+                        const uint64_t b_desc = b_desc0 + s * kStageDesc;
 #pragma unroll
-                    for (int k = 0; k < kBK / 32; ++k) {
-                        // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte units
-                        umma_f8_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
+                        for (int k = 0; k < kBK / 32; ++k) {
+                            // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte units
+                            umma_f8_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
+                        }
+                        // one commit per K block: "MMAs of this block are complete" both frees the smem
+                        // stage for the producer and tells the drain warps the accumulator is ready
+                        tc_commit(&bar_empty[s]);
                     }
-                    // one commit per K block: "MMAs of this block are complete" both frees the smem
-                    // stage for the producer and tells the drain warps the accumulator is ready
-                    tc_commit(&bar_empty[s]);
+                    s += 2; if (s >= static_cast<uint32_t>(S)) { s -= S; ph ^= 1; }
+                    pt ^= 1;
+                    my_it += 2;
                 }
+                it0 = it_end;
             }
         }
       }

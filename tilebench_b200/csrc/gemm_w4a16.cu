@@ -46,20 +46,27 @@ constexpr int kBK = 64;        // K per stage: 64 fp16 = one 128-byte swizzle ro
 constexpr int kWBytes = kBNW * (kBK / 2);   // 4096 packed bytes per weight stage
 constexpr int kGroupN = 16;    // tile-order grouping for L2 reuse
 
-// MT = activation rows per work item = MMA N.
-template <int MT> struct W4Cfg {
+// MT = activation rows per work item = MMA N.  kPair: two CTAs on neighbouring SMs (a cluster of 2) share one
+// work item of 256 weight rows x 256 activation rows: each converts ITS 128 weight rows into its own tensor
+// memory and loads ITS 128 activation rows, and ONE thread of the leader CTA issues cta_group::2 MMAs (M = 256)
+// that read both CTAs' tensor and shared memory — twice the tensor work per issued instruction, which is what
+// the issuing thread of the single-CTA kernel cannot deliver fast enough, and half the activation bytes
+// per SM.
+template <int MT, bool kPair = false> struct W4Cfg {
+    static_assert(!kPair || MT == 256, "the CTA-pair kernel exists for the 256-row tile only");
     // Convert warp groups; group g takes the K blocks with it % kDQ == g.  One group needs about 1 us per K block
     // (barrier hops, LDS, ~140 dependent ALU instructions, tcgen05.st), so two groups deliver a block every
     // ~0.5 us whatever the tile size.  The 128-row tile (one wave of CTAs) is bound by exactly that: three groups
     // were worth 12 %, a fourth another 6 % once it fitted the same 768 threads.  The 256-row tile gains 2-4 %
     // from a third group and loses it again with a fourth (80 registers per thread at 768 threads).
     static constexpr int kDQ = MT == 128 ? 4 : (MT == 256 ? 3 : 2);
-    static constexpr int kActStageBytes = MT * kBK * 2;          // one [MT x 64] fp16 activation tile
+    static constexpr int kActRows = kPair ? MT / 2 : MT;         // activation rows this CTA loads per K block
+    static constexpr int kActStageBytes = kActRows * kBK * 2;    // one [rows x 64] fp16 activation tile
     static constexpr int kNI = MT <= 32 ? 4 : (MT <= 128 ? 2 : 1);   // MMA issuer threads, one accumulator each
     static constexpr int kNAcc = MT >= 128 ? 1 : 2;              // accumulator sets (double-buffered when they fit)
     static constexpr bool kTmaStore = MT >= 128;                 // epilogue through smem + TMA store
     static constexpr int kStoreBytes = kTmaStore ? 128 * kBNW * 2 : 0;   // [128 m x 128 n] fp16 staging tile
-    static constexpr int kSA = MT <= 32 ? 16 : (MT == 64 ? 12 : (MT == 128 ? 8 : 5));   // activation stages
+    static constexpr int kSA = MT <= 32 ? 16 : (MT == 64 ? 12 : (MT == 128 || kPair ? 8 : 5));   // activation stages
     static constexpr int kSW = MT <= 32 ? 32 : (MT == 256 ? 8 : 16);                    // packed-weight stages
     // TMEM operand stages, 32 columns each: as deep as the activation ring, because both are freed by
     // the same per-K-block commit and share its barrier
@@ -149,14 +156,14 @@ __device__ __forceinline__ uint32_t dq_pair(uint32_t lo, uint32_t hi, uint32_t s
 
 using namespace tb200;
 
-template <int MT>
+template <int MT, bool kPair = false>
 __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ tmap_act, const CUtensorMap* __restrict__ tmap_act_half,
                                                 const CUtensorMap* __restrict__ tmap_w, const CUtensorMap* __restrict__ tmap_out,
                                                 const __half* __restrict__ scales, __half* __restrict__ out,
                                                 float* __restrict__ ws, int M, int N, int K, int groups_per_row,
                                                 int kb_per_group, int64_t ldo, int64_t col_offset, int splitk,
                                                 float zp_plus_1024, int tma_store, int tail_split, const PeerOut& peers) {
-    using Cfg = W4Cfg<MT>;
+    using Cfg = W4Cfg<MT, kPair>;
     constexpr int SA = Cfg::kSA;
     constexpr int SW = Cfg::kSW;
     constexpr int AST = Cfg::kAStages;
@@ -181,48 +188,71 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
     uint64_t* bar_dempty = bar_dfull + 2;     // accumulator drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_dempty + 2);
 
-    const int warp = threadIdx.x >> 5;
+    // The warp index and the tensor-memory base are the same in every lane; passing them through a shuffle tells
+    // the compiler so, and everything derived from them (roles, ring slots, descriptors, loop counters) can live
+    // in uniform registers — which is where the MMA and TMA instructions take their operands from.
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
     const int KB = K / kBK;
-    const int tiles_n = N / kBNW;
+    // CTA pair: the work list is walked by pairs; an item's n_blk counts 256-row weight tiles and CTA `rank`
+    // of the pair owns the 128-row half n_blk * 2 + rank
+    const int rank = kPair ? static_cast<int>(cluster_ctarank()) : 0;
+    const int w_first = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int w_step = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    const int tiles_n = N / (kPair ? 2 * kBNW : kBNW);
     const int tiles_m = (M + MT - 1) / MT;
     const Schedule sched = make_schedule(tiles_n, tiles_m, splitk, KB, MT == 256 ? tail_split : 0);
     const int items = sched.items;
+    auto item_of = [&](int w) {
+        Item im = make_item(w, sched);
+        if (kPair) im.n_blk = im.n_blk * 2 + rank;
+        return im;
+    };
     // accumulator of an item and how often it was used before (phase of its barriers)
     auto acc_of = [](uint32_t item_cnt) { return NACC == 1 ? 0 : static_cast<int>(item_cnt & 1); };
     auto acc_use = [](uint32_t item_cnt) { return NACC == 1 ? item_cnt : (item_cnt >> 1); };
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < SA; ++s) { mbar_init(&bar_afull[s], kMerged ? 5 : 1); mbar_init(&bar_done[s], 1); }
+        for (int s = 0; s < SA; ++s) { mbar_init(&bar_afull[s], kMerged ? (kPair ? 9 : 5) : 1); mbar_init(&bar_done[s], 1); }
         for (int s = 0; s < SW; ++s) { mbar_init(&bar_wfull[s], 1); mbar_init(&bar_wempty[s], 4); }
         for (int s = 0; s < AST; ++s) mbar_init(&bar_ofull[s], 4);
-        for (int b = 0; b < 2; ++b) { mbar_init(&bar_dfull[b], NI); mbar_init(&bar_dempty[b], 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&bar_dfull[b], NI); mbar_init(&bar_dempty[b], kPair ? 8 : 4); }
         mbar_fence_init();
         tma_prefetch_desc(tmap_act);
         if (MT == 256 && tail_split > 0) tma_prefetch_desc(tmap_act_half);
         tma_prefetch_desc(tmap_w);
         if (Cfg::kTmaStore && tma_store) tma_prefetch_desc(tmap_out);
     }
+    static_assert(!kPair || kMerged, "the pair kernel uses the merged slot barrier");
     if (warp == 2) {
-        tmem_alloc(tmem_slot, Cfg::kTmemCols);
-        tmem_relinquish();
+        if constexpr (kPair) { tmem_alloc_pair(tmem_slot, Cfg::kTmemCols); tmem_relinquish_pair(); }
+        else { tmem_alloc(tmem_slot, Cfg::kTmemCols); tmem_relinquish(); }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();   // the other CTA's barriers exist before anything signals them
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 
     if (warp == 0) {
         // ---------------- activation TMA producer ----------------
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
-                const Item im = make_item(w, sched);
+            for (int w = w_first; w < items && ok; w += w_step) {
+                const Item im = item_of(w);
                 for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
                     const int s = it % SA;
                     if (!mbar_wait(&bar_done[s], ((it / SA) & 1) ^ 1, ST_WAIT_SMEM_EMPTY, kb)) { ok = false; break; }
-                    if (MT == 256 && im.half >= 0) {      // 128-row unit: the upper or lower half of the stage's box
+                    if constexpr (kPair) {
+                        // this CTA's half of the item's activation rows (128, or 64 of a half-height unit); the bytes
+                        // of both CTAs are counted on the leader's barrier
+                        const bool hu = im.half >= 0;
+                        const uint32_t bytes = hu ? Cfg::kActStageBytes / 2 : Cfg::kActStageBytes;
+                        const int row0 = hu ? im.m_blk * MT + im.half * 128 + rank * 64 : im.m_blk * MT + rank * 128;
+                        if (rank == 0) mbar_expect_tx(&bar_afull[s], 2 * bytes);
+                        tma_load_2d_pair(act_ring + s * Cfg::kActStageBytes, hu ? tmap_act_half : tmap_act, &bar_afull[s], kb * kBK, row0);
+                    } else if (MT == 256 && im.half >= 0) {      // 128-row unit: the upper or lower half of the stage's box
                         mbar_expect_tx(&bar_afull[s], Cfg::kActStageBytes / 2);
                         tma_load_2d(act_ring + s * Cfg::kActStageBytes, tmap_act_half, &bar_afull[s], kb * kBK, im.m_blk * MT + im.half * 128);
                     } else {
@@ -247,8 +277,8 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
-                const Item im = make_item(w, sched);
+            for (int w = w_first; w < items && ok; w += w_step) {
+                const Item im = item_of(w);
                 for (int kb = im.kb0; kb < im.kb1; ++kb, ++it) {
                     const int s = it % SW;
                     if (!mbar_wait(&bar_wempty[s], ((it / SW) & 1) ^ 1, ST_WAIT_SMEM_EMPTY, -kb - 1)) { ok = false; break; }
@@ -265,8 +295,8 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 }
             }
         }
-    } else if (warp >= Cfg::kMmaWarp0 && warp < Cfg::kMmaWarp0 + NI) {
-        // ---------------- MMA issuers ----------------
+    } else if (warp >= Cfg::kMmaWarp0 && warp < Cfg::kMmaWarp0 + NI && rank == 0) {
+        // ---------------- MMA issuers (CTA pair: in the leader CTA only) ----------------
         // The issuing thread is the pacemaker of the large tiles (four MMAs of 128 tensor-pipe cycles each per
         // K block leave it about 500 cycles for everything), so its loop carries no division, no branch
         // that is not needed and no wait that can be avoided: the K blocks of issuer `me` are the running
@@ -281,8 +311,9 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         {
             const bool leader = lane == 0;
             const uint32_t me = warp - Cfg::kMmaWarp0;
-            constexpr uint32_t idesc_full = umma_idesc(0, 0, kBNW, MT);   // f16 x f16 -> f32, M = 128, N = MT
-            constexpr uint32_t idesc_half = umma_idesc(0, 0, kBNW, 128);  // N = 128 for a half unit of the 256-row tile
+            constexpr uint32_t kMmaM = kPair ? 2 * kBNW : kBNW;           // weight rows per MMA (both CTAs of a pair)
+            constexpr uint32_t idesc_full = umma_idesc(0, 0, kMmaM, MT);  // f16 x f16 -> f32, N = MT
+            constexpr uint32_t idesc_half = umma_idesc(0, 0, kMmaM, 128); // N = 128 for a half unit of the 256-row tile
             constexpr uint32_t kStageDesc = Cfg::kActStageBytes >> 4;     // one activation stage in descriptor units
             static_assert(NI <= SA && NI <= AST, "an issuer advances by NI slots per K block");
             const uint64_t b_desc0 = umma_desc_sw128(smem_u32(act_ring));
@@ -293,8 +324,8 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
             uint32_t it0 = 0, item_cnt = 0;
             bool ready = false;                  // my next block's barriers were seen complete already
             bool ok = true;
-            for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++item_cnt) {
-                const Item im = make_item(w, sched);
+            for (int w = w_first; w < items && ok; w += w_step, ++item_cnt) {
+                const Item im = item_of(w);
                 const uint32_t it_end = it0 + static_cast<uint32_t>(im.kb1 - im.kb0);
                 const int acc = acc_of(item_cnt);
                 const uint32_t idesc = (MT == 256 && im.half >= 0) ? idesc_half : idesc_full;
@@ -315,20 +346,31 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                     sa += NI; if (sa >= static_cast<uint32_t>(SA)) { sa -= SA; pa ^= 1; }
                     so += NI; if (so >= static_cast<uint32_t>(AST)) { so -= AST; po ^= 1; }
                     // 16 fp16 of K = 8 TMEM columns of the operand, 32 bytes of the swizzled smem row
-                    if (leader) umma_f16_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+                    if (leader) {
+                        if constexpr (kPair) umma_f16_ts_pair(d_tmem, a_tmem, b_desc, idesc, accumulate);
+                        else umma_f16_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+                    }
                     const bool next_o = kMerged ? true : mbar_test_wait(&bar_ofull[so], po);
                     const bool next_a = mbar_test_wait(&bar_afull[sa], pa);
                     if (leader) {
 #pragma unroll
-                        for (int k = 1; k < kBK / 16; ++k) umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, 1u);
-                        // "MMAs of this K block complete": frees the activation slot and the operand slot
-                        tc_commit(done);
+                        for (int k = 1; k < kBK / 16; ++k) {
+                            if constexpr (kPair) umma_f16_ts_pair(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, 1u);
+                            else umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, 1u);
+                        }
+                        // "MMAs of this K block complete": frees the activation slot and the operand slot (in both
+                        // CTAs of a pair)
+                        if constexpr (kPair) tc_commit_pair(done, 0x3);
+                        else tc_commit(done);
                     }
                     accumulate = 1u;
                     ready = next_o && next_a;
                     my_it += NI;
                 }
-                if (ok && leader) tc_commit(&bar_dfull[acc]);   // one arrival per issuer; every issuer had >= 1 K block
+                if (ok && leader) {                   // one arrival per issuer; every issuer had >= 1 K block
+                    if constexpr (kPair) tc_commit_pair(&bar_dfull[acc], 0x3);
+                    else tc_commit(&bar_dfull[acc]);
+                }
                 it0 = it_end;
             }
         }
@@ -365,21 +407,21 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         while (first_reuse < static_cast<uint32_t>(AST)) first_reuse += DQ;
         uint32_t sd = (first_reuse - AST) % SA, pd = ((first_reuse - AST) / SA) & 1;
         __half s0, s1, s2, n0 = __half(), n1 = __half(), n2 = __half();
-        if (static_cast<int>(blockIdx.x) < items) {
-            const Item im = make_item(blockIdx.x, sched);
+        if (w_first < items) {
+            const Item im = item_of(w_first);
             const __half* srow = scale_row(im);
             const int kbf = im.kb0 + grp;
             n0 = scale_kb(srow, kbf); n1 = scale_kb(srow, kbf + DQ); n2 = scale_kb(srow, kbf + 2 * DQ);
         }
         uint32_t it0 = 0;
         bool ok = true;
-        for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
-            const Item im = make_item(w, sched);
+        for (int w = w_first; w < items && ok; w += w_step) {
+            const Item im = item_of(w);
             const uint32_t it_end = it0 + static_cast<uint32_t>(im.kb1 - im.kb0);
             const __half* srow = scale_row(im);
             s0 = n0; s1 = n1; s2 = n2;
-            if (w + static_cast<int>(gridDim.x) < items) {
-                const Item nx = make_item(w + gridDim.x, sched);
+            if (w + w_step < items) {
+                const Item nx = item_of(w + w_step);
                 const __half* nrow = scale_row(nx);
                 const uint32_t rem = it_end > my_it ? it_end - my_it : 0u;
                 const uint32_t my_next = my_it + (rem + DQ - 1) / DQ * DQ;      // my first K block past this item
@@ -420,7 +462,10 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(kMerged ? &bar_afull[os] : &bar_ofull[os]);
+                if (lane == 0) {
+                    if constexpr (kPair) mbar_arrive_leader(&bar_afull[os]);
+                    else mbar_arrive(kMerged ? &bar_afull[os] : &bar_ofull[os]);
+                }
                 sw += DQ; if (sw >= static_cast<uint32_t>(SW)) { sw -= SW; phw ^= 1; }
                 os += DQ; if (os >= static_cast<uint32_t>(AST)) os -= AST;
             }
@@ -435,8 +480,8 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         uint32_t item_cnt = 0, it0 = 0;
         bool ok = true;
         bool store_pending = false;
-        for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++item_cnt) {
-            const Item im = make_item(w, sched);
+        for (int w = w_first; w < items && ok; w += w_step, ++item_cnt) {
+            const Item im = item_of(w);
             const int acc = acc_of(item_cnt);
             // issuer i wrote its accumulator in this item iff one of the item's K blocks (global
             // numbers it0 .. it0 + len - 1) is congruent to i modulo NI
@@ -490,7 +535,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                         if (h == passes - 1 && c == 3) {     // accumulator fully read: release it
                             tc_fence_before();
                             __syncwarp();
-                            if (lane == 0) mbar_arrive(&bar_dempty[acc]);
+                            if (lane == 0) { if constexpr (kPair) mbar_arrive_leader(&bar_dempty[acc]); else mbar_arrive(&bar_dempty[acc]); }
                         }
 #pragma unroll
                         for (int j = 0; j < 32; ++j) tile[(c * 32 + j) * kBNW + row] = __float2half_rn(__uint_as_float(v[j]));
@@ -519,7 +564,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 if (im.m_blk * MT + (first_half + passes - 1) * 128 >= M) {
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&bar_dempty[acc]);
+                    if (lane == 0) { if constexpr (kPair) mbar_arrive_leader(&bar_dempty[acc]); else mbar_arrive(&bar_dempty[acc]); }
                 }
             } else {
                 const int unit_rows = (MT == 256 && im.half >= 0) ? 128 : MT;
@@ -545,19 +590,22 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_dempty[acc]);
+                if (lane == 0) { if constexpr (kPair) mbar_arrive_leader(&bar_dempty[acc]); else mbar_arrive(&bar_dempty[acc]); }
             }
         }
         if (store_pending && epi_tid == 0) tma_store_wait<0>();   // global writes complete before exit
         if (peers.count > 0) __threadfence_system();              // peer stores visible beyond this GPU
     }
 
+    // (pair: neither CTA may leave while the other can still read its shared or tensor memory or signal its barriers)
     tc_fence_before();
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();
     tc_fence_after();
     if (warp == 2) {
         __syncwarp();
-        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+        if constexpr (kPair) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+        else tmem_dealloc(tmem_base, Cfg::kTmemCols);
     }
 }
 
@@ -574,6 +622,16 @@ TB200_W4_KERNEL(16)
 TB200_W4_KERNEL(64)
 TB200_W4_KERNEL(128)
 TB200_W4_KERNEL(256)
+
+// CTA-pair form of the 256-row tile (see W4Cfg): a cluster of two CTAs per 256 x 256 work item.
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4Cfg<256, true>::kThreads, 1) tb200_k_gemm_w4a16_pair(
+    const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_act_half,
+    const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_out, const __half* scales,
+    __half* out, float* ws, int M, int N, int K, int gpr, int kbpg, int64_t ldo, int64_t col_offset, int splitk,
+    float zp1024, int tma_store, int tail_split, const PeerOut peers) {
+    gemm_w4a16_body<256, true>(&tmap_act, &tmap_act_half, &tmap_w, &tmap_out, scales, out, ws, M, N, K, gpr, kbpg, ldo,
+                               col_offset, splitk, zp1024, tma_store, tail_split, peers);
+}
 
 // out[m, col_offset + n] = fp16( ws[0][m][n] + ws[1][m][n] + ... ) — fixed order, 4 columns per thread.
 extern "C" __global__ void __launch_bounds__(256)
@@ -704,6 +762,64 @@ int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void
     return TB200_OK;
 }
 
+// Launch of the CTA-pair kernel (m > 128, n a multiple of 256, no K split): as many pairs as can be resident at once
+// (one CTA per SM, two SMs per pair), never more than there are work items.  The tail of the persistent schedule is
+// cut into half-height units exactly like the single-CTA kernel's, counted in pairs.
+int launch_w4_pair(const void* a, const void* wp, const void* scales, void* out, int64_t m, int64_t n, int64_t k,
+                   int64_t group, int zp, int64_t ldo, int64_t col_offset, const PeerOut& peers, cudaStream_t st) {
+    using Cfg = W4Cfg<256, true>;
+    static PerDeviceInt max_pairs_tab;
+    int dev = 0;
+    {
+        const int rc_dev = current_device(&dev);
+        if (rc_dev != TB200_OK) return rc_dev;
+    }
+    int max_pairs = max_pairs_tab.v[dev].load(std::memory_order_acquire);
+    if (max_pairs == 0) {
+        TB200_CUDA_TRY(cudaFuncSetAttribute(tb200_k_gemm_w4a16_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(num_sms() & ~1), 1, 1);
+        cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
+        cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+        int clusters = 0;
+        TB200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, tb200_k_gemm_w4a16_pair, &cfg));
+        if (clusters < 1) return fail(TB200_ERR_UNSUPPORTED, "gemm_w4a16: no CTA pair fits on this device");
+        max_pairs = clusters;
+        max_pairs_tab.v[dev].store(clusters, std::memory_order_release);
+    }
+    CUtensorMap ta, tah, tw, to;
+    // this CTA's half of the activation rows of a unit: 128 of 256, or 64 of a 128-row half unit
+    int rc = encode_tmap_2d(&ta, a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, m, k, k * 2, 128, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TB200_OK) return rc;
+    rc = encode_tmap_2d(&tah, a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, m, k, k * 2, 64, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TB200_OK) return rc;
+    rc = encode_tmap_2d(&tw, wp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k / 2, k / 2, kBNW, kBK / 2, CU_TENSOR_MAP_SWIZZLE_32B);
+    if (rc != TB200_OK) return rc;
+    __half* out_slice = static_cast<__half*>(out) + col_offset;
+    rc = encode_tmap_2d(&to, out_slice, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, m, n, ldo * 2, 128, kBNW, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc != TB200_OK) return rc;
+    int64_t items = (n / (2 * kBNW)) * ((m + 255) / 256);
+    int tail_split = 0;
+    {
+        const int64_t rem = items % max_pairs;
+        const char* knob = getenv("TB200_W4_TAIL");
+        if (rem > 0 && 2 * rem <= max_pairs && !(knob && knob[0] == '0')) tail_split = static_cast<int>(rem);
+    }
+    items += tail_split;
+    const int pairs = static_cast<int>(items < max_pairs ? items : max_pairs);
+    tb200_k_gemm_w4a16_pair<<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
+        ta, tah, tw, to, static_cast<const __half*>(scales), static_cast<__half*>(out), nullptr, static_cast<int>(m),
+        static_cast<int>(n), static_cast<int>(k), static_cast<int>(k / group), static_cast<int>(group / kBK), ldo, col_offset, 1,
+        1024.0f + static_cast<float>(zp), 1, tail_split, peers);
+    TB200_CUDA_TRY(cudaGetLastError());
+    return TB200_OK;
+}
+
+// The pair kernel needs whole 256-row weight tiles and the TMA-store epilogue (16-byte aligned slice and pitch).
+bool pair_usable(const void* out, int64_t n, int64_t ldo, int64_t col_offset) {
+    return n % (2 * kBNW) == 0 && ldo % 8 == 0 && aligned16(static_cast<const __half*>(out) + col_offset);
+}
+
 }  // namespace
 
 extern "C" size_t tb200_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
@@ -750,7 +866,14 @@ int gemm_w4a16_impl(const void* a, const void* wp, const void* scales, void* out
         case 16:  return launch_w4<16>(tb200_k_gemm_w4a16_m16, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, peers, st);
         case 64:  return launch_w4<64>(tb200_k_gemm_w4a16_m64, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, peers, st);
         case 128: return launch_w4<128>(tb200_k_gemm_w4a16_m128, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, peers, st);
-        default:  return launch_w4<256>(tb200_k_gemm_w4a16_m256, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, peers, st);
+        default: {
+            // TB200_W4_VARIANT = "pair" | "single" overrides the choice (a tuning and test aid)
+            const char* knob = getenv("TB200_W4_VARIANT");
+            const bool want_pair = knob && knob[0] == 'p';
+            if (want_pair && pair_usable(out, n, ldo, col_offset))
+                return launch_w4_pair(a, wp, scales, out, m, n, k, group, zero_point, ldo, col_offset, peers, st);
+            return launch_w4<256>(tb200_k_gemm_w4a16_m256, a, wp, scales, out, ws, m, n, k, group, zero_point, ldo, col_offset, splitk, peers, st);
+        }
     }
 }
 }  // namespace
