@@ -265,31 +265,43 @@ __device__ __forceinline__ void gemm_plain_body(const CUtensorMap* __restrict__ 
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // The whole warp walks the loop (waits and slot arithmetic are warp-uniform) and lane 0 issues: a lone
+        // thread inside an `if (lane == 0)` region pays 100-250 cycles per branch.  The stage's descriptors are a
+        // base plus a slot offset, the slot and its phase advance by addition, and the next slot's barrier is probed
+        // (non-blocking) between the first and second MMA, so the blocking wait is skipped when the copies are ahead.
+        {
             constexpr uint32_t idesc = pl_idesc(PlainTraits<KIND>::kFmt, kPlBM, BN);
-            uint32_t it = 0, tile_cnt = 0;
+            constexpr uint32_t kStageDesc = Cfg::kStageBytes >> 4;
+            const bool leader = lane == 0;
+            const uint64_t a_desc0 = umma_desc_sw128(smem_u32(smem));
+            const uint64_t b_desc0 = pl_desc_mn_sw128<KIND == PK_TF32>(smem_u32(smem) + Cfg::kABytes, Cfg::kAtomBytes);
+            uint32_t s = 0, ph = 0, tile_cnt = 0;
+            bool ready = false;
             bool ok = true;
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++tile_cnt) {
                 const uint32_t acc = tile_cnt & 1;
                 if (!mbar_wait(&bar_aempty[acc], ((tile_cnt >> 1) & 1) ^ 1, ST_WAIT_TMEM_EMPTY, t)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const int s = it % S;
-                    if (!mbar_wait(&bar_full[s], (it / S) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
+                for (int kb = 0; kb < KB; ++kb) {
+                    if (!ready && !mbar_wait(&bar_full[s], ph, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes);
-                    const uint64_t a_desc = umma_desc_sw128(a_addr);
-                    const uint64_t b_desc = pl_desc_mn_sw128<KIND == PK_TF32>(a_addr + Cfg::kABytes, Cfg::kAtomBytes);
+                    const uint64_t a_desc = a_desc0 + s * kStageDesc;
+                    const uint64_t b_desc = b_desc0 + s * kStageDesc;
+                    uint64_t* const freed = &bar_empty[s];
+                    if (++s == static_cast<uint32_t>(S)) { s = 0; ph ^= 1; }
+                    if (leader) pl_mma<KIND>(d_tmem, a_desc, b_desc, idesc, kb > 0 ? 1u : 0u);
+                    ready = mbar_test_wait(&bar_full[s], ph);
+                    if (leader) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        // a: +32 bytes along K inside the swizzle atom; b: the next kKInst rows of k (16-byte units)
-                        pl_mma<KIND>(d_tmem, a_desc + 2 * k, b_desc + static_cast<uint64_t>(k * Cfg::kKInst * 128 / 16), idesc,
-                                     (kb > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 1; k < 4; ++k) {
+                            // a: +32 bytes along K inside the swizzle atom; b: the next kKInst rows of k (16-byte units)
+                            pl_mma<KIND>(d_tmem, a_desc + 2 * k, b_desc + static_cast<uint64_t>(k * Cfg::kKInst * 128 / 16), idesc, 1u);
+                        }
+                        tc_commit(freed);
                     }
-                    tc_commit(&bar_empty[s]);
                 }
-                if (ok) tc_commit(&bar_afull[acc]);
+                if (ok && leader) tc_commit(&bar_afull[acc]);
             }
         }
     } else if (warp >= 4) {
@@ -435,30 +447,38 @@ __device__ __forceinline__ void gemm_plain_pair_body(const CUtensorMap* __restri
             }
         }
     } else if (warp == 1 && rank == 0) {
-        // ---------------- MMA issuer (leader only) ----------------
-        if (lane == 0) {
+        // ---------------- MMA issuer (leader only; whole warp in the loop, lane 0 issues — see the single-CTA kernel) ----------------
+        {
             constexpr uint32_t idesc = pl_idesc(PlainTraits<KIND>::kFmt, 2 * kPlBM, BN);
-            uint32_t it = 0, tile_cnt = 0;
+            constexpr uint32_t kStageDesc = PCfg::kStageBytes >> 4;
+            const bool leader = lane == 0;
+            const uint64_t a_desc0 = umma_desc_sw128(smem_u32(smem));
+            const uint64_t b_desc0 = pl_desc_mn_sw128<KIND == PK_TF32>(smem_u32(smem) + Cfg::kABytes, Cfg::kAtomBytes);
+            uint32_t s = 0, ph = 0, tile_cnt = 0;
+            bool ready = false;
             bool ok = true;
             for (int t = pair; t < tiles && ok; t += npairs, ++tile_cnt) {
                 const uint32_t acc = tile_cnt & 1;
                 if (!mbar_wait(&bar_aempty[acc], ((tile_cnt >> 1) & 1) ^ 1, ST_WAIT_TMEM_EMPTY, t)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const int s = it % S;
-                    if (!mbar_wait(&bar_full[s], (it / S) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
+                for (int kb = 0; kb < KB; ++kb) {
+                    if (!ready && !mbar_wait(&bar_full[s], ph, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + s * PCfg::kStageBytes);
-                    const uint64_t a_desc = umma_desc_sw128(a_addr);
-                    const uint64_t b_desc = pl_desc_mn_sw128<KIND == PK_TF32>(a_addr + Cfg::kABytes, Cfg::kAtomBytes);
+                    const uint64_t a_desc = a_desc0 + s * kStageDesc;
+                    const uint64_t b_desc = b_desc0 + s * kStageDesc;
+                    uint64_t* const freed = &bar_empty[s];
+                    if (++s == static_cast<uint32_t>(S)) { s = 0; ph ^= 1; }
+                    if (leader) pl_mma_pair<KIND>(d_tmem, a_desc, b_desc, idesc, kb > 0 ? 1u : 0u);
+                    ready = mbar_test_wait(&bar_full[s], ph);
+                    if (leader) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        pl_mma_pair<KIND>(d_tmem, a_desc + 2 * k, b_desc + static_cast<uint64_t>(k * Cfg::kKInst * 128 / 16), idesc,
-                                          (kb > 0 || k > 0) ? 1u : 0u);
-                    tc_commit_pair(&bar_empty[s], 0x3);
+                        for (int k = 1; k < 4; ++k)
+                            pl_mma_pair<KIND>(d_tmem, a_desc + 2 * k, b_desc + static_cast<uint64_t>(k * Cfg::kKInst * 128 / 16), idesc, 1u);
+                        tc_commit_pair(freed, 0x3);
+                    }
                 }
-                if (ok) tc_commit_pair(&bar_afull[acc], 0x3);
+                if (ok && leader) tc_commit_pair(&bar_afull[acc], 0x3);
             }
         }
     } else if (warp >= 4) {
