@@ -434,28 +434,38 @@ tb200_k_gemm_fp8_bs_pair(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
       } else if (warp <= 2 && rank == 0) {
         // ---------------- MMA issuers (leader CTA only; warp 1 even K blocks, warp 2 odd) ----------------
-        if (lane == 0) {
+        // (whole warp in the loop, lane 0 issues; slots by addition — see the single-CTA kernel)
+        {
             constexpr uint32_t idesc = umma_idesc(0, 0, 2 * kBM, BN);
+            constexpr uint32_t kStageDesc = Cfg::kStageBytes >> 4;
+            static_assert(S >= 2 && S % 2 == 0, "two issuers advance by two stages per block");
+            const bool leader = lane == 0;
             const uint32_t me = warp - 1;
-            uint32_t it = 0;
+            const uint64_t a_desc0 = umma_desc_sw128(smem_u32(smem));
+            const uint64_t b_desc0 = umma_desc_sw128(smem_u32(smem) + Cfg::kABytes);
+            const uint32_t d_tmem = tmem_base + me * BN;
+            uint32_t my_it = me, s = me, ph = 0, pt = 1, it0 = 0;
             bool ok = true;
             for (int t = pair; t < tiles && ok; t += npairs) {
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    if ((it & 1) != me) continue;
-                    const int s = it % S;
-                    const int buf = it & 1;
-                    if (!mbar_wait(&bar_tempty[buf], ((it >> 1) & 1) ^ 1, ST_WAIT_TMEM_EMPTY, kb)) { ok = false; break; }
-                    if (!mbar_wait(&bar_full[s], (it / S) & 1, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
+                const uint32_t it_end = it0 + static_cast<uint32_t>(KB);
+                while (my_it < it_end) {
+                    const int kb = static_cast<int>(my_it - it0);
+                    if (!mbar_wait(&bar_tempty[me], pt, ST_WAIT_TMEM_EMPTY, kb)) { ok = false; break; }
+                    if (!mbar_wait(&bar_full[s], ph, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes);
-                    const uint64_t a_desc = umma_desc_sw128(a_addr);
-                    const uint64_t b_desc = umma_desc_sw128(a_addr + Cfg::kABytes);
-                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    if (leader) {
+                        const uint64_t a_desc = a_desc0 + s * kStageDesc;
+                        const uint64_t b_desc = b_desc0 + s * kStageDesc;
 #pragma unroll
-                    for (int k = 0; k < kBK / 32; ++k)
-                        umma_f8_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
-                    tc_commit_pair(&bar_done[s], 0x3);
+                        for (int k = 0; k < kBK / 32; ++k)
+                            umma_f8_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0 ? 1u : 0u);
+                        tc_commit_pair(&bar_done[s], 0x3);
+                    }
+                    s += 2; if (s >= static_cast<uint32_t>(S)) { s -= S; ph ^= 1; }
+                    pt ^= 1;
+                    my_it += 2;
                 }
+                it0 = it_end;
             }
         }
       }
