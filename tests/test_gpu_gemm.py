@@ -268,6 +268,32 @@ def test_w4a16_tail_units_are_bit_identical(cuda_device, monkeypatch, M, N):
         np.testing.assert_allclose(res["1"][0][:, :N].float().cpu().numpy(), want, **FP16_TOL)
 
 
+@pytest.mark.parametrize("M,K,N", [(256, 128, 256), (300, 1024, 2560), (1000, 512, 10240), (4096, 4096, 14336),
+                                   (700, 512, 19200)])
+def test_w4a16_cta_pair_kernel_is_bit_identical(cuda_device, monkeypatch, M, K, N):
+    """The opt-in CTA-pair form of the 256-row tile (TB200_W4_VARIANT=pair: cta_group::2 MMAs over two SMs, each CTA
+    converting its own 128 weight rows) adds the same K blocks in the same order as the single-CTA kernel, so the
+    results must be equal bit for bit — ragged M, half-height tail units (10240 / 256 = 40 and 19200 / 256 = 75 tiles
+    against 74 pairs) and repeated calls included."""
+    ext = native.load()
+    a, wp, sc, group, zp = tensors.generate_gemm_w4a16_inputs(M, K, N, device=cuda_device, seed=M + K + N)
+    native.clear_device_status()
+    res = {}
+    for variant in ("single", "pair"):
+        monkeypatch.setenv("TB200_W4_VARIANT", variant)
+        out = torch.full((M, N + 8), 3.0, dtype=torch.float16, device=cuda_device)
+        ext.gemm_w4a16(a, wp, sc, out, group, zp, 0, None)
+        torch.cuda.synchronize()
+        res[variant] = out
+    for _ in range(5):                                     # still "pair"
+        again = torch.full((M, N + 8), 3.0, dtype=torch.float16, device=cuda_device)
+        ext.gemm_w4a16(a, wp, sc, again, group, zp, 0, None)
+        assert torch.equal(again, res["pair"])
+    status_clean()
+    assert torch.equal(res["single"], res["pair"])
+    assert torch.all(res["pair"][:, N:] == 3.0)
+
+
 @pytest.mark.parametrize("M,K,N,reps", [(4096, 8192, 57344, 60), (128, 4096, 14336, 300), (40, 4096, 14336, 300), (300, 4096, 14336, 200)])
 def test_w4a16_repeated_calls_are_bit_identical(cuda_device, M, K, N, reps):
     """The kernels are deterministic by construction (fixed summation order), so any run-to-run difference is a

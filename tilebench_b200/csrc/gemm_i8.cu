@@ -302,8 +302,15 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
                         rs1 = add_bytes16(v, rs1);
                     }
                 }
+                // The stage may be handed back only when the loads above have LANDED: an arrive that merely follows them
+                // in program order can be issued while they are in flight, and the refill would overtake them.  The
+                // sums depend on every loaded word; ANDed with a zero that only exists at run time (the sign bit of M;
+                // a literal zero would be folded away) they give a zero the hardware can form only after the loads have
+                // returned, and the barrier address depends on it.
+                const uint32_t landed = static_cast<uint32_t>(rs0 ^ rs1) & (static_cast<uint32_t>(M) >> 31);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_empty[s]);        // this warp's rows of the a slices are read
+                if (lane == 0)                                    // this warp's rows of the a slices are read
+                    mbar_arrive(reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(&bar_empty[s]) + landed));
             }
             if (!ok) break;
             const uint32_t rs = static_cast<uint32_t>(rs0 + rs1);

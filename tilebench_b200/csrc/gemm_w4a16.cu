@@ -67,7 +67,13 @@ template <int MT, bool kPair = false> struct W4Cfg {
     static constexpr bool kTmaStore = MT >= 128;                 // epilogue through smem + TMA store
     static constexpr int kStoreBytes = kTmaStore ? 128 * kBNW * 2 : 0;   // [128 m x 128 n] fp16 staging tile
     static constexpr int kSA = MT <= 32 ? 16 : (MT == 64 ? 12 : (MT == 128 || kPair ? 8 : 5));   // activation stages
-    static constexpr int kSW = MT <= 32 ? 32 : (MT == 256 ? 8 : 16);                    // packed-weight stages
+    // packed-weight stages: a multiple of kDQ, so that every slot is always consumed by the SAME convert group.
+    // A group then meets the phases of its slots one by one.  With 8 slots and 3 groups successive uses of a
+    // slot fell to different groups, and a group could test a slot's barrier two phases ahead of it — copies
+    // complete out of order, so "block it - 3 has landed" does not imply "block it - 8 has" — where a
+    // parity test cannot tell "phase k complete" from "phase k - 1 not yet complete": it then read the slot's old
+    // bytes (seen as single output columns differing between identical calls of large problems).
+    static constexpr int kSW = MT <= 32 ? 32 : (MT == 256 ? (kPair ? 9 : 6) : 16);
     // TMEM operand stages, 32 columns each: as deep as the activation ring, because both are freed by
     // the same per-K-block commit and share its barrier
     static constexpr int kAStages = kSA < 8 ? kSA : 8;
@@ -89,6 +95,7 @@ template <int MT, bool kPair = false> struct W4Cfg {
     static constexpr int kBarBytes = 1024;
     static constexpr int kSmemBytes = kActRingBytes + kWRingBytes + kStoreBytes + kBarBytes + 1024;
     static_assert(kAStages <= kSA, "operand ring must not be deeper than the activation ring");
+    static_assert(kSW % kDQ == 0, "each packed-weight slot must belong to one convert group");
     static_assert(kTmemNeed <= 512, "TMEM over-subscribed");
     static_assert((2 * kSA + 2 * kSW + kAStages + 4) * 8 + 8 <= kBarBytes, "barrier block too small");
     static_assert(kSmemBytes <= 232448, "over the 227 KB shared-memory limit");
@@ -384,6 +391,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         // physical offset of this row's two 16-byte chunks under the 32-byte TMA swizzle
         const uint32_t swz = ((row >> 2) & 1) << 4;
         const uint32_t off0 = row * 32 + (0u ^ swz), off1 = row * 32 + (16u ^ swz);
+        const uint32_t rt_zero = static_cast<uint32_t>(M) >> 31;   // 0, but not known to be before the kernel runs
         const int g_last = groups_per_row - 1;
         // scale of this thread's weight row for K block kb (clamped into the row, so look-ahead never leaves it)
         auto scale_kb = [&](const __half* srow, int kb) { return __ldg(srow + min(kb / kb_per_group, g_last)); };
@@ -447,12 +455,18 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                     frag[4 * i + 2] = dq_pair(lo, hi, 0x0602, bias, s2h);
                     frag[4 * i + 3] = dq_pair(lo, hi, 0x0703, bias, s2h);
                 }
-                // The packed stage is released only now, after the unpack has CONSUMED p0 / p1.  Releasing it right
-                // after the two loads were issued let the TMA refill overtake loads still in flight: a few weight
-                // rows of one K block then came from the wrong block (seen as run-to-run differences in single
-                // output columns, about once in twenty calls of a 7168-tile problem with three convert groups).
+                // The packed stage may be released only when p0 / p1 have LANDED in registers.  An arrive that merely
+                // follows the two loads in program order can be issued while they are still in flight, and the TMA
+                // refill then overtakes them: a few weight rows of one K block come from the wrong block (seen as
+                // run-to-run differences in single output columns, about one call in ten of a 7168-tile problem).
+                // Placing the arrive after the unpack is not enough either — compiler and hardware are free to
+                // move register arithmetic across it — so the barrier address is made to DEPEND on the loaded
+                // words: they are ANDed with a zero that only exists at run time (the sign bit of M; a literal zero
+                // would be folded away by the assembler), which the hardware can compute only once both 128-bit loads
+                // have returned (a warp's load completes as a unit, so lane 0 suffices).
+                const uint32_t landed = (p0.x ^ p1.x) & rt_zero;
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_wempty[sw]);
+                if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(&bar_wempty[sw]) + landed));
                 if (my_it >= static_cast<uint32_t>(AST)) {   // the MMAs that last read this operand stage
                     if (!mbar_wait(&bar_done[sd], pd, ST_WAIT_OPERAND, -kb - 1)) { ok = false; break; }
                     sd += DQ; if (sd >= static_cast<uint32_t>(SA)) { sd -= SA; pd ^= 1; }

@@ -104,6 +104,7 @@ __device__ __forceinline__ void gemv_ring_body(const CUtensorMap* __restrict__ t
     uint64_t* bars_all = reinterpret_cast<uint64_t*>(act + Cfg::act_bytes(kpad));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rt_zero = static_cast<uint32_t>(K) >> 31;    // 0, but not known to be before the kernel runs
     const int g = lane >> 2, t = lane & 3;
     const int pair = warp >> 1, kh = warp & 1;                // kh: which half of K this warp sums
     uint8_t* ring = ring_all + warp * ST * kRgBoxBytes;
@@ -127,9 +128,11 @@ __device__ __forceinline__ void gemv_ring_body(const CUtensorMap* __restrict__ t
     // boxes ahead of the consumer.
     uint32_t issued = 0;
     int iss_x = box_lo * 128, iss_y = first_unit * kRgRows, iss_slot = 0;
-    auto issue = [&]() {                                        // lane 0 only
+    // `landed` is a zero derived (in hardware) from words just loaded out of the slot being refilled: the copy's
+    // coordinate depends on it, so the refill cannot be issued while those loads are still in flight.
+    auto issue = [&](uint32_t landed = 0u) {                    // lane 0 only
         mbar_expect_tx(&bars[iss_slot], kRgBoxBytes);
-        tma_load_2d(ring + iss_slot * kRgBoxBytes, tmap_w, &bars[iss_slot], iss_x, iss_y);
+        tma_load_2d(ring + iss_slot * kRgBoxBytes, tmap_w, &bars[iss_slot], iss_x + static_cast<int>(landed), iss_y);
         ++issued;
         iss_slot = iss_slot + 1 == ST ? 0 : iss_slot + 1;
         iss_x += 128;
@@ -227,10 +230,12 @@ __device__ __forceinline__ void gemv_ring_body(const CUtensorMap* __restrict__ t
             next_scales(nl[1], nh[1]);
             if (!mbar_wait(&bars[slot], phase, ST_WAIT_SMEM_FULL, st)) { ok = false; break; }
             const uint32_t box = ring_base + slot * kRgBoxBytes;
+            uint32_t touched = 0u;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const uint4 wl = lds128<0>(box + (h == 0 ? woff0 : woff1));
                 const uint4 wh = lds128<1024>(box + (h == 0 ? woff0 : woff1));
+                touched ^= wl.x ^ wh.x;
                 const __half2 s_lo = __half2half2(sl[h]), s_hi = __half2half2(sh[h]);
                 const uint32_t wdl[4] = {wl.x, wl.y, wl.z, wl.w}, wdh[4] = {wh.x, wh.y, wh.z, wh.w};
 #pragma unroll
@@ -255,8 +260,14 @@ __device__ __forceinline__ void gemv_ring_body(const CUtensorMap* __restrict__ t
             }
             sl[0] = nl[0]; sl[1] = nl[1]; sh[0] = nh[0]; sh[1] = nh[1];
             a_addr += kActStage;
+            // The slot may be refilled only when the four loads from it have LANDED in registers; following them in
+            // program order is not enough (the copy could be issued while they are in flight, and the unpack
+            // arithmetic may be moved across it).  The loaded words are ANDed with a zero that only exists at run time
+            // (a literal zero would be folded away by the assembler), so the result is a zero the hardware can form
+            // only once the loads have returned; a warp's load completes as a unit, so lane 0's registers speak for all.
+            const uint32_t landed = touched & rt_zero;
             __syncwarp();                                       // every lane has read the slot
-            if (lane == 0 && issued < total) issue();           // refill it: the slot just read is the next to fill
+            if (lane == 0 && issued < total) issue(landed);     // refill it: the slot just read is the next to fill
             if (++slot == ST) { slot = 0; phase ^= 1; }
         }
         // upper half -> shared memory; lower half adds it (own sum first) and writes the unit's outputs.  One named
