@@ -292,6 +292,7 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
                 const int s = n % S;
                 if (!mbar_wait(&bar_full[s], (n / S) & 1, ST_WAIT_SMEM_FULL, ks)) { ok = false; break; }
                 const uint8_t* a_row = smem + s * Cfg::kStageBytes + row_off;
+                uint32_t touched = 0u;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
 #pragma unroll
@@ -300,14 +301,16 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
                         const uint4 v = *reinterpret_cast<const uint4*>(a_row + i * kI8APlaneBytes + (((c + 1) ^ key) << 4));
                         rs0 = add_bytes16(u, rs0);
                         rs1 = add_bytes16(v, rs1);
+                        touched ^= u.x ^ v.x;
                     }
                 }
                 // The stage may be handed back only when the loads above have LANDED: an arrive that merely follows them
-                // in program order can be issued while they are in flight, and the refill would overtake them.  The
-                // sums depend on every loaded word; ANDed with a zero that only exists at run time (the sign bit of M;
+                // in program order can be issued while they are in flight, and the refill would overtake them.  One word
+                // of every load is folded into `touched` (not the sums: their dependent chains are long, and the
+                // stage would be held for their whole length); ANDed with a zero that only exists at run time (the sign bit of M;
                 // a literal zero would be folded away) they give a zero the hardware can form only after the loads have
                 // returned, and the barrier address depends on it.
-                const uint32_t landed = static_cast<uint32_t>(rs0 ^ rs1) & (static_cast<uint32_t>(M) >> 31);
+                const uint32_t landed = touched & (static_cast<uint32_t>(M) >> 31);
                 __syncwarp();
                 if (lane == 0)                                    // this warp's rows of the a slices are read
                     mbar_arrive(reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(&bar_empty[s]) + landed));
