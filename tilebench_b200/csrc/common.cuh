@@ -295,6 +295,28 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
         : "memory");
 }
 
+// Predicated forms for loops that the whole warp walks while one lane issues: every lane executes the
+// statement, the instruction itself is guarded by `issue` (true in one lane), so the loop needs no
+// divergent branch around its issue instructions.
+__device__ __forceinline__ void umma_f16_ts_if(uint32_t issue, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(issue)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_if(uint32_t issue, uint64_t* bar) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(smem_u32(bar)), "r"(issue)
+        : "memory");
+}
+
 // ---- CTA pairs (cta_group::2): one MMA spans two SMs; the even CTA of the pair is the leader ----
 // A shared-memory address of the executing CTA, as returned by smem_u32(), carries the CTA's rank in
 // the cluster in bit 24; clearing it addresses the same offset in the even (leader) CTA of the pair.

@@ -353,25 +353,29 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                     sa += NI; if (sa >= static_cast<uint32_t>(SA)) { sa -= SA; pa ^= 1; }
                     so += NI; if (so >= static_cast<uint32_t>(AST)) { so -= AST; po ^= 1; }
                     // 16 fp16 of K = 8 TMEM columns of the operand, 32 bytes of the swizzled smem row
-                    if (leader) {
-                        if constexpr (kPair) umma_f16_ts_pair(d_tmem, a_tmem, b_desc, idesc, accumulate);
-                        else umma_f16_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+                    if constexpr (kPair) {
+                        if (leader) umma_f16_ts_pair(d_tmem, a_tmem, b_desc, idesc, accumulate);
+                    } else {
+                        umma_f16_ts_if(leader, d_tmem, a_tmem, b_desc, idesc, accumulate);
                     }
                     const bool next_o = kMerged ? true : mbar_test_wait(&bar_ofull[so], po);
                     const bool next_a = mbar_test_wait(&bar_afull[sa], pa);
-                    if (leader) {
+                    if constexpr (kPair) {
+                        if (leader) {
 #pragma unroll
-                        for (int k = 1; k < kBK / 16; ++k) {
-                            if constexpr (kPair) umma_f16_ts_pair(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, 1u);
-                            else umma_f16_ts(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, 1u);
+                            for (int k = 1; k < kBK / 16; ++k) umma_f16_ts_pair(d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, 1u);
+                            tc_commit_pair(done, 0x3);   // arrives in both CTAs of the pair
                         }
-                        // "MMAs of this K block complete": frees the activation slot and the operand slot (in both
-                        // CTAs of a pair)
-                        if constexpr (kPair) tc_commit_pair(done, 0x3);
-                        else tc_commit(done);
+                    } else {
+                        // predicated, not branched: only lane 0's instructions take effect
+#pragma unroll
+                        for (int k = 1; k < kBK / 16; ++k) umma_f16_ts_if(leader, d_tmem, a_tmem + 8 * k, b_desc + 2 * k, idesc, 1u);
+                        // "MMAs of this K block complete": frees the activation slot and the operand slot
+                        tc_commit_if(leader, done);
                     }
                     accumulate = 1u;
-                    ready = next_o && next_a;
+                    // one answer for the whole warp, so that the branch on it is uniform
+                    ready = __all_sync(0xffffffffu, next_o && next_a);
                     my_it += NI;
                 }
                 if (ok && leader) {                   // one arrival per issuer; every issuer had >= 1 K block
