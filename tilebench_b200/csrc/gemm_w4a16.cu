@@ -374,8 +374,9 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                         tc_commit_if(leader, done);
                     }
                     accumulate = 1u;
-                    // one answer for the whole warp, so that the branch on it is uniform
-                    ready = __all_sync(0xffffffffu, next_o && next_a);
+                    // (per lane, no warp vote: the lanes agree in practice, and a vote would have to wait for lanes whose
+                    // bounded wait gave up in the rare case that others' succeeded)
+                    ready = next_o && next_a;
                     my_it += NI;
                 }
                 if (ok && leader) {                   // one arrival per issuer; every issuer had >= 1 K block
