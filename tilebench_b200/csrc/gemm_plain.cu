@@ -87,36 +87,36 @@ __host__ __device__ constexpr uint32_t pl_idesc(uint32_t fmt, uint32_t m, uint32
     return (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 template <int KIND>
-__device__ __forceinline__ void pl_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void pl_mma(uint32_t issue, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     if constexpr (KIND == PK_F16 || KIND == PK_BF16) {
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
-                     "r"(idesc), "r"(accumulate) : "memory");
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+                     "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
+                     "r"(idesc), "r"(accumulate), "r"(issue) : "memory");
     } else if constexpr (KIND == PK_TF32) {
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                     "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
-                     "r"(idesc), "r"(accumulate) : "memory");
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+                     "@q tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
+                     "r"(idesc), "r"(accumulate), "r"(issue) : "memory");
     } else {
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                     "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
-                     "r"(idesc), "r"(accumulate) : "memory");
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+                     "@q tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
+                     "r"(idesc), "r"(accumulate), "r"(issue) : "memory");
     }
 }
 
 template <int KIND>
-__device__ __forceinline__ void pl_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void pl_mma_pair(uint32_t issue, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     if constexpr (KIND == PK_F16 || KIND == PK_BF16) {
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                     "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
-                     "r"(idesc), "r"(accumulate) : "memory");
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+                     "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
+                     "r"(idesc), "r"(accumulate), "r"(issue) : "memory");
     } else if constexpr (KIND == PK_TF32) {
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                     "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
-                     "r"(idesc), "r"(accumulate) : "memory");
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+                     "@q tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
+                     "r"(idesc), "r"(accumulate), "r"(issue) : "memory");
     } else {
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                     "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
-                     "r"(idesc), "r"(accumulate) : "memory");
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+                     "@q tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
+                     "r"(idesc), "r"(accumulate), "r"(issue) : "memory");
     }
 }
 
@@ -290,16 +290,15 @@ __device__ __forceinline__ void gemm_plain_body(const CUtensorMap* __restrict__ 
                     const uint64_t b_desc = b_desc0 + s * kStageDesc;
                     uint64_t* const freed = &bar_empty[s];
                     if (++s == static_cast<uint32_t>(S)) { s = 0; ph ^= 1; }
-                    if (leader) pl_mma<KIND>(d_tmem, a_desc, b_desc, idesc, kb > 0 ? 1u : 0u);
+                    // predicated, not branched: every lane runs the statements, lane 0's instructions take effect
+                    pl_mma<KIND>(leader, d_tmem, a_desc, b_desc, idesc, kb > 0 ? 1u : 0u);
                     ready = mbar_test_wait(&bar_full[s], ph);
-                    if (leader) {
 #pragma unroll
-                        for (int k = 1; k < 4; ++k) {
-                            // a: +32 bytes along K inside the swizzle atom; b: the next kKInst rows of k (16-byte units)
-                            pl_mma<KIND>(d_tmem, a_desc + 2 * k, b_desc + static_cast<uint64_t>(k * Cfg::kKInst * 128 / 16), idesc, 1u);
-                        }
-                        tc_commit(freed);
+                    for (int k = 1; k < 4; ++k) {
+                        // a: +32 bytes along K inside the swizzle atom; b: the next kKInst rows of k (16-byte units)
+                        pl_mma<KIND>(leader, d_tmem, a_desc + 2 * k, b_desc + static_cast<uint64_t>(k * Cfg::kKInst * 128 / 16), idesc, 1u);
                     }
+                    tc_commit_if(leader, freed);
                 }
                 if (ok && leader) tc_commit(&bar_afull[acc]);
             }
@@ -469,14 +468,12 @@ __device__ __forceinline__ void gemm_plain_pair_body(const CUtensorMap* __restri
                     const uint64_t b_desc = b_desc0 + s * kStageDesc;
                     uint64_t* const freed = &bar_empty[s];
                     if (++s == static_cast<uint32_t>(S)) { s = 0; ph ^= 1; }
-                    if (leader) pl_mma_pair<KIND>(d_tmem, a_desc, b_desc, idesc, kb > 0 ? 1u : 0u);
+                    pl_mma_pair<KIND>(leader, d_tmem, a_desc, b_desc, idesc, kb > 0 ? 1u : 0u);
                     ready = mbar_test_wait(&bar_full[s], ph);
-                    if (leader) {
 #pragma unroll
-                        for (int k = 1; k < 4; ++k)
-                            pl_mma_pair<KIND>(d_tmem, a_desc + 2 * k, b_desc + static_cast<uint64_t>(k * Cfg::kKInst * 128 / 16), idesc, 1u);
-                        tc_commit_pair(freed, 0x3);
-                    }
+                    for (int k = 1; k < 4; ++k)
+                        pl_mma_pair<KIND>(leader, d_tmem, a_desc + 2 * k, b_desc + static_cast<uint64_t>(k * Cfg::kKInst * 128 / 16), idesc, 1u);
+                    if (leader) tc_commit_pair(freed, 0x3);
                 }
                 if (ok && leader) tc_commit_pair(&bar_afull[acc], 0x3);
             }
