@@ -181,8 +181,10 @@ int    tb200_gemm_w4a16(const void* a, const void* wp, const void* scales, void*
  * the reference has no multi-GPU path).  Rank `rank` of `world` owns weight rows
  * [rank * n_local, (rank + 1) * n_local); out_ptrs[r] is rank r's full output [m, ldo] (fp16, ldo >= world *
  * n_local), peer-mapped into this process for r != rank (symmetric memory / CUDA IPC).  The epilogue stores
- * every finished tile into columns [rank * n_local, ...) of ALL `world` buffers — its own by TMA store, the
- * others by 128-bit peer stores over NVLink — so the transfer overlaps the main loop.  Needs m > 64 and
+ * every finished tile into columns [rank * n_local, ...) of ALL `world` buffers by TMA stores (one tensor map per
+ * rank's slice; plain bulk stores, nothing is loaded from a peer and nothing is multicast; the environment
+ * knob TB200_W4_GATHER=stores makes the epilogue threads push the tile with 128-bit stores instead) — so the
+ * transfer overlaps the main loop.  Needs m > 64 and
  * 16-byte aligned slices (TB200_ERR_UNSUPPORTED otherwise: gather with NCCL instead).  Callers must put a
  * cross-rank barrier between this call and any read of the gathered buffer.  out_ptrs is a HOST array.
  */

@@ -106,7 +106,13 @@ template <int MT, bool kPair = false> struct W4Cfg {
 constexpr int kMaxPeers = 7;
 struct PeerOut {
     int count;
+    int use_tma;                 // 1: the tiles go to the peers as TMA stores through PeerMaps, 0: as 128-bit stores from the epilogue threads
     __half* base[kMaxPeers];
+};
+// One tensor map per peer output slice (same geometry as the local one): the epilogue then hands a finished tile to
+// the copy engine once per rank instead of pushing it through the NVLink with its own threads' stores.
+struct PeerMaps {
+    CUtensorMap m[kMaxPeers];
 };
 
 // half < 0: the item covers all MT activation rows of tile m_blk; half = 0 / 1: a 128-row half of a 256-row
@@ -169,7 +175,8 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                                                 const __half* __restrict__ scales, __half* __restrict__ out,
                                                 float* __restrict__ ws, int M, int N, int K, int groups_per_row,
                                                 int kb_per_group, int64_t ldo, int64_t col_offset, int splitk,
-                                                float zp_plus_1024, int tma_store, int tail_split, const PeerOut& peers) {
+                                                float zp_plus_1024, int tma_store, int tail_split, const PeerOut& peers,
+                                                const PeerMaps* __restrict__ peer_maps) {
     using Cfg = W4Cfg<MT, kPair>;
     constexpr int SA = Cfg::kSA;
     constexpr int SW = Cfg::kSW;
@@ -563,10 +570,12 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     if (epi_tid == 0) {
                         tma_store_2d(tmap_out, tile, im.n_blk * kBNW, row0);
+                        if (peers.use_tma)      // the same tile to every other rank, in the same bulk group (plain stores, no multicast)
+                            for (int p = 0; p < peers.count; ++p) tma_store_2d(&peer_maps->m[p], tile, im.n_blk * kBNW, row0);
                         tma_store_commit();
                     }
                     store_pending = true;
-                    if (peers.count > 0) {
+                    if (peers.count > 0 && !peers.use_tma) {
                         // the same tile to every other rank: 16 threads write one 256-byte row, 128-bit stores
                         const int rows_valid = min(128, M - row0);
                         for (int p = 0; p < peers.count; ++p) {
@@ -633,9 +642,10 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_act_half,           \
         const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_out,                  \
         const __half* scales, __half* out, float* ws, int M, int N, int K, int gpr, int kbpg, int64_t ldo,         \
-        int64_t col_offset, int splitk, float zp1024, int tma_store, int tail_split, const PeerOut peers) {        \
+        int64_t col_offset, int splitk, float zp1024, int tma_store, int tail_split, const PeerOut peers,          \
+        const __grid_constant__ PeerMaps peer_maps) {                                                              \
         gemm_w4a16_body<MT>(&tmap_act, &tmap_act_half, &tmap_w, &tmap_out, scales, out, ws, M, N, K, gpr, kbpg,    \
-                            ldo, col_offset, splitk, zp1024, tma_store, tail_split, peers);                        \
+                            ldo, col_offset, splitk, zp1024, tma_store, tail_split, peers, &peer_maps);            \
     }
 TB200_W4_KERNEL(16)
 TB200_W4_KERNEL(64)
@@ -647,9 +657,9 @@ extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4Cfg<256
     const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_act_half,
     const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_out, const __half* scales,
     __half* out, float* ws, int M, int N, int K, int gpr, int kbpg, int64_t ldo, int64_t col_offset, int splitk,
-    float zp1024, int tma_store, int tail_split, const PeerOut peers) {
+    float zp1024, int tma_store, int tail_split, const PeerOut peers, const __grid_constant__ PeerMaps peer_maps) {
     gemm_w4a16_body<256, true>(&tmap_act, &tmap_act_half, &tmap_w, &tmap_out, scales, out, ws, M, N, K, gpr, kbpg, ldo,
-                               col_offset, splitk, zp1024, tma_store, tail_split, peers);
+                               col_offset, splitk, zp1024, tma_store, tail_split, peers, &peer_maps);
 }
 
 // out[m, col_offset + n] = fp16( ws[0][m][n] + ws[1][m][n] + ... ) — fixed order, 4 columns per thread.
@@ -721,6 +731,18 @@ int pick_splitk(int64_t m, int64_t n, int64_t k) {
     return best;
 }
 
+// Tensor maps of the peers' output slices ([m, n] fp16 at peers.base[p], row pitch ldo; 128 x 128 boxes like the local one).
+int encode_peer_maps(PeerMaps* pm, const PeerOut& peers, int64_t m, int64_t n, int64_t ldo) {
+    memset(pm, 0, sizeof(*pm));
+    if (!peers.use_tma) return TB200_OK;
+    for (int p = 0; p < peers.count; ++p) {
+        const int rc = encode_tmap_2d(&pm->m[p], peers.base[p], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, m, n, ldo * 2, 128, kBNW,
+                                      CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc != TB200_OK) return rc;
+    }
+    return TB200_OK;
+}
+
 template <int MT, typename Kern>
 int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void* out, float* ws, int64_t m, int64_t n,
               int64_t k, int64_t group, int zp, int64_t ldo, int64_t col_offset, int splitk, const PeerOut& peers,
@@ -763,11 +785,14 @@ int launch_w4(Kern kern, const void* a, const void* wp, const void* scales, void
         }
     }
     items += tail_split;
+    PeerMaps pm;
+    rc = encode_peer_maps(&pm, peers, m, n, ldo);
+    if (rc != TB200_OK) return rc;
     const int grid = static_cast<int>(items < num_sms() ? items : num_sms());
     kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(ta, tah, tw, to, static_cast<const __half*>(scales), static_cast<__half*>(out), ws,
                                                         static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
                                                         static_cast<int>(k / group), static_cast<int>(group / kBK), ldo,
-                                                        col_offset, splitk, 1024.0f + static_cast<float>(zp), tma_store, tail_split, peers);
+                                                        col_offset, splitk, 1024.0f + static_cast<float>(zp), tma_store, tail_split, peers, pm);
     TB200_CUDA_TRY(cudaGetLastError());
     if (splitk > 1) {
         const int64_t total = m * (n / 4);
@@ -825,11 +850,14 @@ int launch_w4_pair(const void* a, const void* wp, const void* scales, void* out,
         if (rem > 0 && 2 * rem <= max_pairs && !(knob && knob[0] == '0')) tail_split = static_cast<int>(rem);
     }
     items += tail_split;
+    PeerMaps pm;
+    rc = encode_peer_maps(&pm, peers, m, n, ldo);
+    if (rc != TB200_OK) return rc;
     const int pairs = static_cast<int>(items < max_pairs ? items : max_pairs);
     tb200_k_gemm_w4a16_pair<<<2 * pairs, Cfg::kThreads, Cfg::kSmemBytes, st>>>(
         ta, tah, tw, to, static_cast<const __half*>(scales), static_cast<__half*>(out), nullptr, static_cast<int>(m),
         static_cast<int>(n), static_cast<int>(k), static_cast<int>(k / group), static_cast<int>(group / kBK), ldo, col_offset, 1,
-        1024.0f + static_cast<float>(zp), 1, tail_split, peers);
+        1024.0f + static_cast<float>(zp), 1, tail_split, peers, pm);
     TB200_CUDA_TRY(cudaGetLastError());
     return TB200_OK;
 }
@@ -921,6 +949,9 @@ extern "C" int tb200_gemm_w4a16_gather(const void* a, const void* wp_local, cons
         if (!aligned16(base)) return fail(TB200_ERR_ALIGN, "gemm_w4a16_gather: peer output slices must be 16-byte aligned");
         peers.base[peers.count++] = base;
     }
+    // TB200_W4_GATHER=stores: the epilogue threads' own 128-bit peer stores instead of TMA stores (a tuning and test aid)
+    const char* gk = getenv("TB200_W4_GATHER");
+    peers.use_tma = (gk && gk[0] == 's') ? 0 : 1;
     return gemm_w4a16_impl(a, wp_local, scales_local, out_ptrs[rank], m, n_local, k, group, zero_point, ldo, col_offset,
                            nullptr, 0, peers, stream);
 }
