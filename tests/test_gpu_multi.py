@@ -35,10 +35,16 @@ def _rank_main(rank, world, port, out_dir):
         fused = npart.gemm_w4a16_partitioned(a, wp[lo:hi], sc[lo:hi], group, zp, gather="fused")
         torch.cuda.synchronize()
         fused_copy = fused.clone()
-        again = npart.gemm_w4a16_partitioned(a, wp[lo:hi], sc[lo:hi], group, zp, gather="fused")
+        again = npart.gemm_w4a16_partitioned(a, wp[lo:hi], sc[lo:hi], group, zp, gather="fused").clone()
         torch.cuda.synchronize()
+        # the same fused gather with the tiles pushed by the epilogue threads' own stores instead of TMA stores
+        os.environ["TB200_W4_GATHER"] = "stores"
+        by_threads = npart.gemm_w4a16_partitioned(a, wp[lo:hi], sc[lo:hi], group, zp, gather="fused").clone()
+        torch.cuda.synchronize()
+        os.environ.pop("TB200_W4_GATHER")
         assert native.device_status()[0] == 0
-        torch.save({"nccl": via_nccl.cpu(), "push": pushed.cpu(), "fused": fused_copy.cpu(), "again": again.cpu()}, os.path.join(out_dir, f"r{rank}.pt"))
+        torch.save({"nccl": via_nccl.cpu(), "push": pushed.cpu(), "fused": fused_copy.cpu(), "again": again.cpu(),
+                    "by_threads": by_threads.cpu()}, os.path.join(out_dir, f"r{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -59,3 +65,4 @@ def test_two_gpu_partitioned_gemm_gathers_agree(tmp_path):
         assert torch.equal(got["push"], single), f"rank {r}: push gather differs from the single-GPU result"
         assert torch.equal(got["fused"], single), f"rank {r}: fused gather differs from the single-GPU result"
         assert torch.equal(got["again"], single)
+        assert torch.equal(got["by_threads"], single), f"rank {r}: fused gather by thread stores differs"
