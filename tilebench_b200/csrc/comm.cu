@@ -71,8 +71,11 @@ extern "C" int tb200_allgather_cols(const void* local, int64_t ld_local, void* c
         return fail(TB200_ERR_ALIGN, "allgather_cols: slices, pitches and pointers must be multiples of 16 bytes");
     GatherDst dst{};
     const uint8_t* src = static_cast<const uint8_t*>(local);
-    for (int r = 0; r < world; ++r) {
+    for (int r = 0; r < world; ++r)
         if (!out_ptrs[r]) return fail(TB200_ERR_ARG, "allgather_cols: null output pointer for rank %d", r);
+    // destinations in the order rank, rank + 1, ... (mod world): at any moment the ranks then store to DIFFERENT GPUs
+    for (int i = 0; i < world; ++i) {
+        const int r = (rank + i) % world;
         uint8_t* base = static_cast<uint8_t*>(out_ptrs[r]) + static_cast<int64_t>(rank) * row_bytes;
         if (!aligned16(base)) return fail(TB200_ERR_ALIGN, "allgather_cols: output of rank %d is not 16-byte aligned", r);
         if (r == rank && base == src) continue;            // the slice was computed in place

@@ -942,9 +942,12 @@ extern "C" int tb200_gemm_w4a16_gather(const void* a, const void* wp_local, cons
         return fail(TB200_ERR_ARG, "gemm_w4a16_gather: ldo=%lld < world*n_local=%lld", (long long)ldo, (long long)(world * n_local));
     const int64_t col_offset = static_cast<int64_t>(rank) * n_local;
     PeerOut peers{};
-    for (int r = 0; r < world; ++r) {
+    for (int r = 0; r < world; ++r)
         if (!out_ptrs[r]) return fail(TB200_ERR_ARG, "gemm_w4a16_gather: null output pointer for rank %d", r);
-        if (r == rank) continue;
+    // peers in the order rank + 1, rank + 2, ... (mod world): at any moment the ranks then store to DIFFERENT
+    // destinations instead of all starting with rank 0
+    for (int i = 1; i < world; ++i) {
+        const int r = (rank + i) % world;
         __half* base = static_cast<__half*>(out_ptrs[r]) + col_offset;
         if (!aligned16(base)) return fail(TB200_ERR_ALIGN, "gemm_w4a16_gather: peer output slices must be 16-byte aligned");
         peers.base[peers.count++] = base;
