@@ -406,7 +406,12 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         const uint32_t rt_zero = static_cast<uint32_t>(M) >> 31;   // 0, but not known to be before the kernel runs
         const int g_last = groups_per_row - 1;
         // scale of this thread's weight row for K block kb (clamped into the row, so look-ahead never leaves it)
-        auto scale_kb = [&](const __half* srow, int kb) { return __ldg(srow + min(kb / kb_per_group, g_last)); };
+        // (K blocks per scale group are a power of two for every group size in use: a shift instead of a division)
+        const int kbpg_shift = (kb_per_group & (kb_per_group - 1)) == 0 ? 31 - __clz(kb_per_group) : -1;
+        auto scale_kb = [&](const __half* srow, int kb) {
+            const int g = kbpg_shift >= 0 ? kb >> kbpg_shift : kb / kb_per_group;
+            return __ldg(srow + min(g, g_last));
+        };
         auto scale_row = [&](const Item& im) {
             return scales + static_cast<int64_t>(im.n_blk * kBNW + row) * groups_per_row;
         };
