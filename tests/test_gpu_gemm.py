@@ -205,14 +205,16 @@ def test_w4a16_matches_oracle_across_m(cuda_device, M):
 
 
 @pytest.mark.parametrize("M", [8, 24, 300])
-@pytest.mark.parametrize("group", [64, 256])
+@pytest.mark.parametrize("group", [64, 192, 256])
 def test_w4a16_other_group_sizes_follow_the_workspace_query(cuda_device, M, group):
-    """Groups of 64 (not a multiple of 128: decode-sized m takes the tensor-memory kernel instead of the streaming
-    one) and 256, through impl_cuda.run, i.e. with exactly the workspace the query reports."""
-    got, want = w4_case(M, 1024, 1024, seed=90 + M + group, device=cuda_device, group=group)
+    """Groups of 64 and 192 (not multiples of 128: decode-sized m takes the tensor-memory kernel instead of the
+    streaming one; 192 = three K blocks per group, the one size whose scale index needs a division) and 256, through
+    impl_cuda.run, i.e. with exactly the workspace the query reports."""
+    K = 1536 if group == 192 else 1024
+    got, want = w4_case(M, 1024, K, seed=90 + M + group, device=cuda_device, group=group)
     np.testing.assert_allclose(got, want, **FP16_TOL)
     # the benchmark's weight shape, where the split-K choice is the interesting one
-    got, want = w4_case(M, 14336, 1024, seed=91 + M + group, device=cuda_device, group=group)
+    got, want = w4_case(M, 14336, K, seed=91 + M + group, device=cuda_device, group=group)
     np.testing.assert_allclose(got, want, **FP16_TOL)
 
 
