@@ -164,12 +164,12 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t n = 0;                                       // stages issued so far
+            uint32_t s = 0, ph = 0;                               // ring slot and phase of stage n, advanced by addition
             bool ok = true;
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
                 const int m_blk = t % tiles_m, n_blk = t / tiles_m;
-                for (int ks = 0; ks < KS; ++ks, ++n) {
-                    const int s = n % S;
-                    if (!mbar_wait(&bar_empty[s], ((n / S) & 1) ^ 1, ST_WAIT_SMEM_EMPTY, ks)) { ok = false; break; }
+                for (int ks = 0; ks < KS; ++ks, ++n, s = (s + 1 == S ? 0 : s + 1), ph ^= (s == 0)) {
+                    if (!mbar_wait(&bar_empty[s], ph ^ 1, ST_WAIT_SMEM_EMPTY, ks)) { ok = false; break; }
                     uint8_t* stage = smem + s * Cfg::kStageBytes;
                     const int kb0 = ks * kI8StageRows;
                     mbar_expect_tx(&bar_full[s], Cfg::kStageBytes);
@@ -181,10 +181,10 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
             }
             if (!ok) {
                 // give copies already in flight a bounded chance to land before the CTA exits
-                for (int s = 0; s < S; ++s) {
-                    if (n > static_cast<uint32_t>(s)) {
-                        const uint32_t last = n - 1 - ((n - 1 - s) % S);
-                        (void)mbar_wait(&bar_full[s], (last / S) & 1, ST_WAIT_SMEM_FULL, -1);
+                for (int st = 0; st < S; ++st) {
+                    if (n > static_cast<uint32_t>(st)) {
+                        const uint32_t last = n - 1 - ((n - 1 - st) % S);
+                        (void)mbar_wait(&bar_full[st], (last / S) & 1, ST_WAIT_SMEM_FULL, -1);
                     }
                 }
             }
@@ -197,14 +197,14 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
             const uint32_t d_tmem = tmem_base + me * BN;
             const uint32_t u_addr = smem_u32(ubuf + 2 * me * Cfg::kGroupBufBytes);
             uint32_t n = 0;                                       // stages seen so far (= own sub-steps)
+            uint32_t s = 0, ph = 0;                               // ring slot and phase of stage n, advanced by addition
             uint32_t tile_cnt = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++tile_cnt) {
                 if (!mbar_wait(bar_aempty, (tile_cnt & 1) ^ 1, ST_WAIT_TMEM_EMPTY, t)) { ok = false; break; }
                 tc_fence_after();
-                for (int ks = 0; ks < KS; ++ks, ++n) {
-                    const int s = n % S;
-                    if (!mbar_wait(&bar_full[s], (n / S) & 1, ST_WAIT_SMEM_FULL, ks)) { ok = false; break; }
+                for (int ks = 0; ks < KS; ++ks, ++n, s = (s + 1 == S ? 0 : s + 1), ph ^= (s == 0)) {
+                    if (!mbar_wait(&bar_full[s], ph, ST_WAIT_SMEM_FULL, ks)) { ok = false; break; }
                     const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes) + me * kI8SubRows;   // +32 B along K
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {                 // the two groups of this sub-step
@@ -236,11 +236,11 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
         const int gt = threadIdx.x - (4 + g * Cfg::kGroupWarps) * 32;
         uint8_t* dst = ubuf + g * Cfg::kGroupBufBytes;
         uint32_t n = 0;
+        uint32_t s = 0, ph = 0;                                   // ring slot and phase of stage n, advanced by addition
         bool ok = true;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-            for (int ks = 0; ks < KS && ok; ++ks, ++n) {
-                const int s = n % S;
-                if (!mbar_wait(&bar_full[s], (n / S) & 1, ST_WAIT_SMEM_FULL, ks)) { ok = false; break; }
+            for (int ks = 0; ks < KS && ok; ++ks, ++n, s = (s + 1 == S ? 0 : s + 1), ph ^= (s == 0)) {
+                if (!mbar_wait(&bar_full[s], ph, ST_WAIT_SMEM_FULL, ks)) { ok = false; break; }
                 const uint8_t* packed = smem + s * Cfg::kStageBytes + kI8ABytes + j * kI8SubRows * BN;
                 uint4 w[kPerThread];
 #pragma unroll
@@ -283,14 +283,15 @@ __device__ __forceinline__ void gemm_i8_body(const CUtensorMap* __restrict__ tma
         const int row = ew * 32 + lane;
         const uint32_t row_off = row * 64, key = (row >> 1) & 3;
         uint32_t tile_cnt = 0, n = 0;
+        uint32_t es = 0, eph = 0;                                 // ring slot and phase of stage n, advanced by addition
         bool ok = true;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++tile_cnt) {
             const int m_blk = t % tiles_m, n_blk = t / tiles_m;
             const int m = m_blk * kI8BM + row;
             int32_t rs0 = 0, rs1 = 0;                              // sum_k a[m, k] (rows past M are zero-filled by TMA)
-            for (int ks = 0; ks < KS; ++ks, ++n) {
-                const int s = n % S;
-                if (!mbar_wait(&bar_full[s], (n / S) & 1, ST_WAIT_SMEM_FULL, ks)) { ok = false; break; }
+            for (int ks = 0; ks < KS; ++ks, ++n, es = (es + 1 == S ? 0 : es + 1), eph ^= (es == 0)) {
+                const uint32_t s = es;
+                if (!mbar_wait(&bar_full[s], eph, ST_WAIT_SMEM_FULL, ks)) { ok = false; break; }
                 const uint8_t* a_row = smem + s * Cfg::kStageBytes + row_off;
                 uint32_t touched = 0u;
 #pragma unroll
