@@ -256,12 +256,15 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
                 const uint32_t it_end = it0 + static_cast<uint32_t>(KB);
                 while (my_it < it_end) {
                     const int kb = static_cast<int>(my_it - it0);
-                    if (!mbar_wait(&bar_tempty[me], pt, ST_WAIT_TMEM_EMPTY, kb)) { ok = false; break; }
+                    // The operands first (they are there long before, and even a satisfied wait costs about 90 cycles),
+                    // the accumulator buffer last: "buffer released -> first MMA issued" is part of the dependency loop
+                    // that paces the kernel, and only the fence now stands between the two.
                     if (!mbar_wait(&bar_full[s], ph, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
+                    const uint64_t a_desc = a_desc0 + s * kStageDesc;
+                    const uint64_t b_desc = b_desc0 + s * kStageDesc;
+                    if (!mbar_wait(&bar_tempty[me], pt, ST_WAIT_TMEM_EMPTY, kb)) { ok = false; break; }
                     tc_fence_after();
                     if (leader) {
-                        const uint64_t a_desc = a_desc0 + s * kStageDesc;
-                        const uint64_t b_desc = b_desc0 + s * kStageDesc;
 #pragma unroll
                         for (int k = 0; k < kBK / 32; ++k) {
                             // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte units
