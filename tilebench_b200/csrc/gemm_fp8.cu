@@ -91,8 +91,8 @@ __device__ __forceinline__ bool drain_tile(uint64_t* bar_done, uint64_t* bar_tem
             tmem_ld32(taddr + c * 64 + 32, v1);
             tmem_wait_ld();
             if (c == 1) {                                        // everything is in registers: free the buffer
+                // (tcgen05.wait::ld is warp-collective: every lane's loads have completed, no further warp barrier needed)
                 tc_fence_before();
-                __syncwarp();
                 if (lane == 0) {
                     if constexpr (kPair) mbar_arrive_leader(&bar_tempty[it & 1]);
                     else mbar_arrive(&bar_tempty[it & 1]);
