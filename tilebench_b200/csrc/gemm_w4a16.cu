@@ -490,9 +490,8 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 }
                 tc_fence_after();
                 tmem_st32(t_lane + os * 32, frag);
-                tmem_wait_st();
+                tmem_wait_st();                                  // warp-collective: every lane's stores have completed
                 tc_fence_before();
-                __syncwarp();
                 if (lane == 0) {
                     if constexpr (kPair) mbar_arrive_leader(&bar_afull[os]);
                     else mbar_arrive(kMerged ? &bar_afull[os] : &bar_ofull[os]);
