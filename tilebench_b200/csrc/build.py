@@ -90,6 +90,31 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     return out
 
 
+def build_variant(tag: str, defines: list[str], sources: list[str], verbose: bool = False) -> Path:
+    """libtb200_<tag>.so next to the normal library: the normal objects, with `sources` recompiled with -D<defines>.
+    For diagnostic builds (e.g. TB200_ROLE_CYCLES); the product library is never replaced."""
+    build_library(verbose=verbose)                      # the other objects come from the normal build
+    out = LIB_DIR / f"libtb200_{tag}.so"
+    stamp = LIB_DIR / f"libtb200_{tag}.sha256"
+    want = _digest(existing_sources() + list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h"))) + " " + " ".join(defines + sources)
+    if out.exists() and stamp.exists() and stamp.read_text().strip() == want:
+        return out
+    var_dir = OBJ_DIR / f"variant_{tag}"
+    var_dir.mkdir(parents=True, exist_ok=True)
+    flags = NVCC_FLAGS + [f"-D{d}" for d in defines]
+    objs = []
+    for src in existing_sources():
+        if src.name in sources:
+            obj = var_dir / (src.stem + ".o")
+            _run([_nvcc(), *flags, "-I", INCLUDE, "-c", src, "-o", obj], verbose)
+        else:
+            obj = OBJ_DIR / (src.stem + ".o")
+        objs.append(obj)
+    _run([_nvcc(), "-shared", "-o", out, *objs], verbose)
+    stamp.write_text(want)
+    return out
+
+
 def extension_path() -> Path:
     suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
     return LIB_DIR / (EXT_STEM + suffix)

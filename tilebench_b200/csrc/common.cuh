@@ -127,6 +127,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Role cycle accounting (build variant -DTB200_ROLE_CYCLES, see tilebench_b200/profiling/role_cycles.py): statements
+// wrapped in TB200_RC(...) exist only in that variant; the normal library contains none of them.
+#ifdef TB200_ROLE_CYCLES
+#define TB200_RC(...) __VA_ARGS__
+#else
+#define TB200_RC(...)
+#endif
+
 // Non-blocking probe of a phase (mbarrier.test_wait never suspends the thread): used to look at the NEXT
 // stage's barriers between two instructions of the current one, so that the probe's latency is hidden and
 // the blocking wait below is skipped when the answer was already "complete".

@@ -169,6 +169,24 @@ __device__ __forceinline__ uint32_t dq_pair(uint32_t lo, uint32_t hi, uint32_t s
 
 using namespace tb200;
 
+#ifdef TB200_ROLE_CYCLES
+// Sums of clock64 intervals per role, CTA 0 only.  [0..6] issuer (all issuer warps): loop back edge, wait (blocking, only
+// when the probe said "not ready"), fence, first MMA, probes + slot arithmetic, remaining MMAs + commit, K blocks;
+// [8..13] convert warps of TMEM lane quarter 0 (one per group): wait for the packed stage, loads + unpack + release,
+// wait for the operand slot, tcgen05.st + arrive, loop overhead between visits, visits; [16] cycles from kernel start to
+// the end of CTA 0's epilogue, [17] work items of CTA 0, [18] cycles the issuer spent between items.
+__device__ unsigned long long g_w4_role_cycles[32];
+extern "C" int tb200_w4a16_role_cycles(unsigned long long* host32, int clear) {
+    if (cudaMemcpyFromSymbol(host32, g_w4_role_cycles, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
+    if (clear) {
+        unsigned long long z[32] = {};
+        if (cudaMemcpyToSymbol(g_w4_role_cycles, z, sizeof(z)) != cudaSuccess) return 1;
+    }
+    return 0;
+}
+#define TB200_RC_ADD(slot, v) atomicAdd(&g_w4_role_cycles[slot], static_cast<unsigned long long>(v))
+#endif
+
 template <int MT, bool kPair = false>
 __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ tmap_act, const CUtensorMap* __restrict__ tmap_act_half,
                                                 const CUtensorMap* __restrict__ tmap_w, const CUtensorMap* __restrict__ tmap_out,
@@ -247,6 +265,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
     if constexpr (kPair) cluster_sync_all();   // the other CTA's barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+    TB200_RC(const long long rc_start = clock64(); const bool rc_on = blockIdx.x == 0;)
 
     if (warp == 0) {
         // ---------------- activation TMA producer ----------------
@@ -338,6 +357,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
             uint32_t it0 = 0, item_cnt = 0;
             bool ready = false;                  // my next block's barriers were seen complete already
             bool ok = true;
+            TB200_RC(long long rc[7] = {0, 0, 0, 0, 0, 0, 0}; long long rc_prev = 0, rc_item = 0, rc_between = 0;)
             for (int w = w_first; w < items && ok; w += w_step, ++item_cnt) {
                 const Item im = item_of(w);
                 const uint32_t it_end = it0 + static_cast<uint32_t>(im.kb1 - im.kb0);
@@ -347,13 +367,17 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 // the accumulator set must have been drained before this item's first MMA overwrites it
                 if (!mbar_wait(&bar_dempty[acc], (acc_use(item_cnt) & 1) ^ 1, ST_WAIT_TMEM_EMPTY, w)) { ok = false; break; }
                 uint32_t accumulate = 0u;
+                TB200_RC(if (rc_item) rc_between += clock64() - rc_item; rc_prev = 0;)
                 while (my_it < it_end) {
+                    TB200_RC(const long long q0 = clock64(); if (rc_prev) rc[0] += q0 - rc_prev;)
                     if (!ready) {
                         const int kb = im.kb0 + static_cast<int>(my_it - it0);
                         if (!kMerged && !mbar_wait(&bar_ofull[so], po, ST_WAIT_OPERAND, kb)) { ok = false; break; }
                         if (!mbar_wait(&bar_afull[sa], pa, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
                     }
+                    TB200_RC(const long long q1 = clock64();)
                     tc_fence_after();
+                    TB200_RC(const long long q2 = clock64();)
                     const uint32_t a_tmem = a_tmem0 + so * 32;
                     const uint64_t b_desc = b_desc0 + sa * kStageDesc;
                     uint64_t* const done = &bar_done[sa];
@@ -365,8 +389,10 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                     } else {
                         umma_f16_ts_if(leader, d_tmem, a_tmem, b_desc, idesc, accumulate);
                     }
+                    TB200_RC(const long long q3 = clock64();)
                     const bool next_o = kMerged ? true : mbar_test_wait(&bar_ofull[so], po);
                     const bool next_a = mbar_test_wait(&bar_afull[sa], pa);
+                    TB200_RC(asm volatile("" ::"r"(static_cast<int>(next_o)), "r"(static_cast<int>(next_a)) : "memory"); const long long q4 = clock64();)
                     if constexpr (kPair) {
                         if (leader) {
 #pragma unroll
@@ -385,13 +411,18 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                     // bounded wait gave up in the rare case that others' succeeded)
                     ready = next_o && next_a;
                     my_it += NI;
+                    TB200_RC(const long long q5 = clock64(); rc[1] += q1 - q0; rc[2] += q2 - q1; rc[3] += q3 - q2; rc[4] += q4 - q3;
+                             rc[5] += q5 - q4; rc[6] += 1; rc_prev = q5;)
                 }
+                TB200_RC(rc_item = clock64();)
                 if (ok && leader) {                   // one arrival per issuer; every issuer had >= 1 K block
                     if constexpr (kPair) tc_commit_pair(&bar_dfull[acc], 0x3);
                     else tc_commit(&bar_dfull[acc]);
                 }
                 it0 = it_end;
             }
+            TB200_RC(if (rc_on && leader) { for (int i = 0; i < 7; ++i) TB200_RC_ADD(i, rc[i]);
+                                            if (me == 0) { TB200_RC_ADD(17, item_cnt); TB200_RC_ADD(18, rc_between); } })
         }
     } else if (warp >= Cfg::kCvtWarp0 && warp < Cfg::kEpiWarp0) {
         // ---------------- convert warps: packed int4 (smem) -> fp16 operand (TMEM) ----------------
@@ -440,6 +471,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
         }
         uint32_t it0 = 0;
         bool ok = true;
+        TB200_RC(long long rc[6] = {0, 0, 0, 0, 0, 0}; long long rc_prev = 0;)
         for (int w = w_first; w < items && ok; w += w_step) {
             const Item im = item_of(w);
             const uint32_t it_end = it0 + static_cast<uint32_t>(im.kb1 - im.kb0);
@@ -457,7 +489,9 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 const int kb = im.kb0 + static_cast<int>(my_it - it0);
                 const __half s_cur = s0;
                 s0 = s1; s1 = s2; s2 = scale_kb(srow, kb + 3 * DQ);
+                TB200_RC(const long long q0 = clock64(); if (rc_prev) rc[4] += q0 - rc_prev;)
                 if (!mbar_wait(&bar_wfull[sw], phw, ST_WAIT_SMEM_FULL, kb)) { ok = false; break; }
+                TB200_RC(const long long q1 = clock64();)
                 const uint8_t* wt = w_ring + sw * kWBytes;
                 const uint4 p0 = *reinterpret_cast<const uint4*>(wt + off0);
                 const uint4 p1 = *reinterpret_cast<const uint4*>(wt + off1);
@@ -484,10 +518,12 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 const uint32_t landed = (p0.x ^ p1.x) & rt_zero;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(&bar_wempty[sw]) + landed));
+                TB200_RC(asm volatile("" ::"r"(frag[0]), "r"(frag[15]), "r"(frag[31]) : "memory"); const long long q2 = clock64();)
                 if (my_it >= static_cast<uint32_t>(AST)) {   // the MMAs that last read this operand stage
                     if (!mbar_wait(&bar_done[sd], pd, ST_WAIT_OPERAND, -kb - 1)) { ok = false; break; }
                     sd += DQ; if (sd >= static_cast<uint32_t>(SA)) { sd -= SA; pd ^= 1; }
                 }
+                TB200_RC(const long long q3 = clock64();)
                 tc_fence_after();
                 tmem_st32(t_lane + os * 32, frag);
                 tmem_wait_st();                                  // warp-collective: every lane's stores have completed
@@ -498,9 +534,12 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
                 }
                 sw += DQ; if (sw >= static_cast<uint32_t>(SW)) { sw -= SW; phw ^= 1; }
                 os += DQ; if (os >= static_cast<uint32_t>(AST)) os -= AST;
+                TB200_RC(const long long q4 = clock64(); rc[0] += q1 - q0; rc[1] += q2 - q1; rc[2] += q3 - q2; rc[3] += q4 - q3;
+                         rc[5] += 1; rc_prev = q4;)
             }
             it0 = it_end;
         }
+        TB200_RC(if (rc_on && lane == 0 && lane_grp == 0) for (int i = 0; i < 6; ++i) TB200_RC_ADD(8 + i, rc[i]);)
     } else if (warp >= Cfg::kEpiWarp0) {
         // ---------------- epilogue warps ----------------
         const int lane_grp = warp & 3;
@@ -626,6 +665,7 @@ __device__ __forceinline__ void gemm_w4a16_body(const CUtensorMap* __restrict__ 
             }
         }
         if (store_pending && epi_tid == 0) tma_store_wait<0>();   // global writes complete before exit
+        TB200_RC(if (rc_on && epi_tid == 0) TB200_RC_ADD(16, clock64() - rc_start);)
         if (peers.count > 0) __threadfence_system();              // peer stores visible beyond this GPU
     }
 
