@@ -44,3 +44,14 @@ def test_capture_validation_names_foreign_kernels():
         ncu_one.validate_capture(CSV, "gemm_w4a16")
     with pytest.raises(RuntimeError, match="nothing was captured"):
         ncu_one.validate_capture([["ID", "Kernel Name"], ["", ""]], "gemm_w4a16")
+
+
+def test_role_cycle_variant_adds_its_reader_and_leaves_the_product_library_alone():
+    """The diagnostic build (-DTB200_ROLE_CYCLES) is a separate library with one extra entry point; the product library
+    does not export it (its exports are pinned against include/tb200.h in test_abi.py)."""
+    import ctypes
+    from tilebench_b200.csrc import build
+    variant = ctypes.CDLL(str(build.build_variant("role_cycles", ["TB200_ROLE_CYCLES=1"], ["gemm_w4a16.cu"])))
+    assert hasattr(variant, "tb200_w4a16_role_cycles") and hasattr(variant, "tb200_gemm_w4a16")
+    product = ctypes.CDLL(str(build.build_library()))
+    assert not hasattr(product, "tb200_w4a16_role_cycles")
