@@ -51,7 +51,9 @@ def test_role_cycle_variant_adds_its_reader_and_leaves_the_product_library_alone
     does not export it (its exports are pinned against include/tb200.h in test_abi.py)."""
     import ctypes
     from tilebench_b200.csrc import build
-    variant = ctypes.CDLL(str(build.build_variant("role_cycles", ["TB200_ROLE_CYCLES=1"], ["gemm_w4a16.cu"])))
-    assert hasattr(variant, "tb200_w4a16_role_cycles") and hasattr(variant, "tb200_gemm_w4a16")
+    from tilebench_b200.profiling import role_cycles
+    variant = ctypes.CDLL(str(build.build_variant("role_cycles", ["TB200_ROLE_CYCLES=1"], role_cycles.VARIANT_SOURCES)))
+    assert hasattr(variant, "tb200_w4a16_role_cycles") and hasattr(variant, "tb200_fp8_role_cycles")
+    assert hasattr(variant, "tb200_gemm_w4a16")
     product = ctypes.CDLL(str(build.build_library()))
-    assert not hasattr(product, "tb200_w4a16_role_cycles")
+    assert not hasattr(product, "tb200_w4a16_role_cycles") and not hasattr(product, "tb200_fp8_role_cycles")

@@ -16,6 +16,23 @@
 #include <cstdlib>
 #include <cstring>
 
+#ifdef TB200_ROLE_CYCLES
+// Sums of clock64 intervals, CTA 0 only (build variant, see tilebench_b200/profiling/role_cycles.py).  [0..7] first drain
+// warp per K block: wait for the MMAs, first batch of TMEM loads, its FMAs, second batch of loads, release, its FMAs,
+// loop top, K blocks; [8..11] both issuing threads per own K block: waits (operands, then the accumulator buffer),
+// fence + four MMAs + commit, loop overhead, K blocks.
+__device__ unsigned long long g_fp8_role_cycles[32];
+extern "C" int tb200_fp8_role_cycles(unsigned long long* host32, int clear) {
+    if (cudaMemcpyFromSymbol(host32, g_fp8_role_cycles, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
+    if (clear) {
+        unsigned long long z[32] = {};
+        if (cudaMemcpyToSymbol(g_fp8_role_cycles, z, sizeof(z)) != cudaSuccess) return 1;
+    }
+    return 0;
+}
+#define TB200_RC_ADD8(slot, v) atomicAdd(&g_fp8_role_cycles[slot], static_cast<unsigned long long>(v))
+#endif
+
 namespace tb200 {
 namespace {
 
@@ -76,11 +93,14 @@ __device__ __forceinline__ bool drain_tile(uint64_t* bar_done, uint64_t* bar_tem
     float pa0 = __ldg(sa_row), pb0 = __ldg(sb_row);
     float pa1 = KB > 1 ? __ldg(sa_row + 1) : 0.f, pb1 = KB > 1 ? __ldg(sb_row + 1) : 0.f;
     float pa2 = KB > 2 ? __ldg(sa_row + 2) : 0.f, pb2 = KB > 2 ? __ldg(sb_row + 2) : 0.f;
+    TB200_RC(long long rc[7] = {0, 0, 0, 0, 0, 0, 0}; long long rc_prev = 0;)
     for (int kb = 0; kb < KB; ++kb, ++it) {
+        TB200_RC(const long long qa = clock64(); if (rc_prev) rc[6] += qa - rc_prev;)
         const uint32_t taddr = t_lane + (it & 1) * BN;
         float pa3 = 0.f, pb3 = 0.f;
         if (kb + 3 < KB) { pa3 = __ldg(sa_row + kb + 3); pb3 = __ldg(sb_row + kb + 3); }
         if (!mbar_wait(&bar_done[it % S], (it / S) & 1, ST_WAIT_TMEM_FULL, kb)) return false;
+        TB200_RC(long long qc = clock64(); rc[0] += qc - qa;)
         tc_fence_after();
         const float sc = pa0 * pb0;
         const float2 sc2 = make_float2(sc, sc);
@@ -90,6 +110,7 @@ __device__ __forceinline__ bool drain_tile(uint64_t* bar_done, uint64_t* bar_tem
             tmem_ld32(taddr + c * 64, v0);
             tmem_ld32(taddr + c * 64 + 32, v1);
             tmem_wait_ld();
+            TB200_RC({ const long long q = clock64(); rc[c == 0 ? 1 : 3] += q - qc; qc = q; })
             if (c == 1) {                                        // everything is in registers: free the buffer
                 // (tcgen05.wait::ld is warp-collective: every lane's loads have completed, no further warp barrier needed)
                 tc_fence_before();
@@ -97,6 +118,7 @@ __device__ __forceinline__ bool drain_tile(uint64_t* bar_done, uint64_t* bar_tem
                     if constexpr (kPair) mbar_arrive_leader(&bar_tempty[it & 1]);
                     else mbar_arrive(&bar_tempty[it & 1]);
                 }
+                TB200_RC({ const long long q = clock64(); rc[4] += q - qc; qc = q; })
             }
             // two IEEE FMAs per instruction (fma.rn.f32x2): half the issue slots of the scalar form, same results
 #pragma unroll
@@ -113,11 +135,15 @@ __device__ __forceinline__ bool drain_tile(uint64_t* bar_done, uint64_t* bar_tem
                 acc[c * 64 + 32 + j] = r.x;
                 acc[c * 64 + 32 + j + 1] = r.y;
             }
+            TB200_RC({ asm volatile("" ::"f"(acc[c * 64]), "f"(acc[c * 64 + 31]), "f"(acc[c * 64 + 33]), "f"(acc[c * 64 + 63]) : "memory");
+                       const long long q = clock64(); rc[c == 0 ? 2 : 5] += q - qc; qc = q; })
         }
+        TB200_RC(rc_prev = qc;)
         pa0 = pa1; pb0 = pb1;
         pa1 = pa2; pb1 = pb2;
         pa2 = pa3; pb2 = pb3;
     }
+    TB200_RC(if (blockIdx.x == 0 && threadIdx.x == 128) { for (int i = 0; i < 7; ++i) TB200_RC_ADD8(i, rc[i]); TB200_RC_ADD8(7, KB); })
     return true;
 }
 
@@ -251,11 +277,13 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
             uint32_t my_it = me, s = me, ph = 0, pt = 1;               // pt: phase to wait for on "buffer free"
             uint32_t it0 = 0;
             bool ok = true;
+            TB200_RC(long long rc[4] = {0, 0, 0, 0}; long long rc_prev = 0;)
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
                 const uint32_t idesc = u < wide_units ? idesc_wide : idesc_half;
                 const uint32_t it_end = it0 + static_cast<uint32_t>(KB);
                 while (my_it < it_end) {
                     const int kb = static_cast<int>(my_it - it0);
+                    TB200_RC(const long long q0 = clock64(); if (rc_prev) rc[2] += q0 - rc_prev;)
                     // The operands first (they are there long before, and even a satisfied wait costs about 90 cycles),
                     // the accumulator buffer last: "buffer released -> first MMA issued" is part of the dependency loop
                     // that paces the kernel, and only the fence now stands between the two.
@@ -263,6 +291,7 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
                     const uint64_t a_desc = a_desc0 + s * kStageDesc;
                     const uint64_t b_desc = b_desc0 + s * kStageDesc;
                     if (!mbar_wait(&bar_tempty[me], pt, ST_WAIT_TMEM_EMPTY, kb)) { ok = false; break; }
+                    TB200_RC(const long long q1 = clock64();)
                     tc_fence_after();
                     if (leader) {
 #pragma unroll
@@ -277,9 +306,11 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* __restrict__ tm
                     s += 2; if (s >= static_cast<uint32_t>(S)) { s -= S; ph ^= 1; }
                     pt ^= 1;
                     my_it += 2;
+                    TB200_RC(const long long q2 = clock64(); rc[0] += q1 - q0; rc[1] += q2 - q1; rc[3] += 1; rc_prev = q2;)
                 }
                 it0 = it_end;
             }
+            TB200_RC(if (blockIdx.x == 0 && leader) { TB200_RC_ADD8(8, rc[0]); TB200_RC_ADD8(9, rc[1]); TB200_RC_ADD8(10, rc[2]); TB200_RC_ADD8(11, rc[3]); })
         }
       }
     } else {
